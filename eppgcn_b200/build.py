@@ -1,0 +1,100 @@
+"""In-tree build of the native pieces.
+
+``libeppgcn_b200.so``  the C-ABI library (CUDA kernels for sm_100a + host
+                       helpers), compiled with nvcc; no torch headers.
+``GNNAdvisor*.so``     the torch extension that exposes the reference's
+                       operator API on top of the C-ABI library.
+
+Both land next to this file so they travel with the source tree.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB_NAME = "libeppgcn_b200.so"
+LIB_PATH = os.path.join(HERE, LIB_NAME)
+EXT_NAME = "GNNAdvisor"
+EXT_PATH = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+LIB_SOURCES = ["spmm.cu", "prep.cu", "host.cu"]
+
+
+def _nvcc() -> str:
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        raise RuntimeError("nvcc not found; the CUDA toolkit is required to build eppgcn_b200")
+    return nvcc
+
+
+def _stale(target: str, sources: list[str]) -> bool:
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    return any(os.path.getmtime(s) > t for s in sources)
+
+
+def _run(cmd: list[str], verbose: bool):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("build failed:\n" + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    if verbose and (r.stdout or r.stderr):
+        print(r.stdout + r.stderr, flush=True)
+
+
+def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
+    srcs = [os.path.join(CSRC, s) for s in LIB_SOURCES]
+    deps = srcs + [os.path.join(CSRC, "common.cuh"),
+                   os.path.join(HERE, "..", "include", "eppgcn_b200.h"), __file__]
+    if force or _stale(LIB_PATH, deps):
+        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+        if ptxas_info:
+            flags += ["-Xptxas", "-v"]
+        _run([_nvcc(), *flags, "-shared", "-o", LIB_PATH, *srcs], verbose or ptxas_info)
+    return LIB_PATH
+
+
+def build_extension(force: bool = False, verbose: bool = False) -> str:
+    """g++ build of the pybind/torch layer; links the C-ABI library by rpath."""
+    build_library(force=False, verbose=verbose)
+    src = os.path.join(CSRC, "gnnadvisor_ext.cpp")
+    deps = [src, os.path.join(HERE, "..", "include", "eppgcn_b200.h"), __file__]
+    if not (force or _stale(EXT_PATH, deps)):
+        return EXT_PATH
+    import torch
+    from torch.utils.cpp_extension import include_paths, library_paths
+    inc = include_paths("cuda") if "cuda" in include_paths.__code__.co_varnames else include_paths()
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    if os.path.join(cuda_home, "include") not in inc:
+        inc.append(os.path.join(cuda_home, "include"))
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden",
+           f"-DTORCH_EXTENSION_NAME={EXT_NAME}", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch.compiled_with_cxx11_abi())}",
+           "-I" + sysconfig.get_paths()["include"], *["-I" + p for p in inc],
+           "-I" + os.path.join(HERE, "..", "include"),
+           src, "-o", EXT_PATH,
+           "-L" + HERE, "-leppgcn_b200", "-Wl,-rpath,$ORIGIN",
+           "-L" + torch_lib, "-Wl,-rpath," + torch_lib,
+           "-lc10", "-ltorch_cpu", "-ltorch", "-ltorch_python", "-lc10_cuda", "-ltorch_cuda",
+           "-L" + os.path.join(cuda_home, "lib64"), "-lcudart"]
+    _run(cmd, verbose)
+    return EXT_PATH
+
+
+def build_all(force: bool = False, verbose: bool = False):
+    build_library(force, verbose)
+    build_extension(force, verbose)
+
+
+if __name__ == "__main__":
+    build_all(force="--force" in sys.argv, verbose=True)

@@ -1,0 +1,231 @@
+"""ctypes binding of ``libeppgcn_b200.so`` (declared in ``include/eppgcn_b200.h``).
+
+This is the thin layer the tests and the benchmark use to drive the C-ABI
+directly with torch tensors as device buffers.  There is no CPU fallback: a
+missing library, or a device entry point given a non-CUDA tensor, raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libeppgcn_b200.so")
+
+EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE = range(5)
+
+_P, _I, _LL, _SZ = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
+
+# name -> (restype, argtypes); mirrors include/eppgcn_b200.h one to one.
+SIGNATURES = {
+    "eppgcn_version": (_I, []),
+    "eppgcn_status_string": (C.c_char_p, [_I]),
+    "eppgcn_last_error": (C.c_char_p, []),
+    "eppgcn_spmm_forward": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_spmm_backward_compacted": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
+    "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
+    "eppgcn_split_scratch_bytes": (_SZ, [_I]),
+    "eppgcn_split_parts": (_I, [_P, _I, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
+    "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
+    "eppgcn_build_part_host": (_I, [_I, _P, _I, _P, _P, C.POINTER(_LL)]),
+    "eppgcn_map_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
+    "eppgcn_bucket_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
+    "eppgcn_get_ginfo_host": (_I, [_P, _I, _I, _P]),
+    "eppgcn_timing_enable": (_I, [_I]),
+    "eppgcn_time_begin": (_I, [_P]),
+    "eppgcn_time_end": (_I, [_I, _I, _I, _P]),
+    "eppgcn_time_read": (_I, [_P]),
+    "eppgcn_print_time": (_I, []),
+    "eppgcn_clear_time": (_I, []),
+}
+
+_lib = None
+
+
+class EppError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"eppgcn_b200 status {status}: {message}")
+        self.status = status
+
+
+def lib() -> C.CDLL:
+    """Loads the library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: run `python -m eppgcn_b200.build` (there is no CPU fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(status: int):
+    if status != EPP_OK:
+        l = lib()
+        raise EppError(status, f"{l.eppgcn_status_string(status).decode()}: {l.eppgcn_last_error().decode()}")
+
+
+def _dev(t: torch.Tensor | None, dtype, name: str):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _row_stride(t: torch.Tensor, name: str) -> int:
+    if t.dim() != 2 or not t.is_cuda or t.dtype != torch.float32 or (t.size(1) > 1 and t.stride(1) != 1):
+        raise RuntimeError(f"{name} must be a 2-D fp32 CUDA tensor with unit column stride")
+    return t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
+
+
+def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size=0, dim_worker=32,
+                 warp_per_block=8, out=None, deg_row=None):
+    """``out = diag(deg_row) A diag(degrees) feat`` over the CSR; ``feat`` may
+    have a padded row stride."""
+    n = row_ptr.numel() - 1
+    dim = feat.size(1)
+    ld = _row_stride(feat, "feat")
+    if out is None:
+        out = torch.empty(n, dim, device=feat.device, dtype=torch.float32)
+    deg_row = degrees if deg_row is None else deg_row
+    check(lib().eppgcn_spmm_forward(
+        _dev(out, torch.float32, "out"), feat.data_ptr(), ld,
+        _dev(row_ptr, torch.int32, "row_ptr"), _dev(col_idx, torch.int32, "col_idx"),
+        _dev(deg_row, torch.float32, "deg_row"), _dev(degrees, torch.float32, "degrees"),
+        _dev(part_ptr, torch.int32, "part_ptr"), _dev(part2node, torch.int32, "part2node"),
+        n, dim, part2node.numel(), part_size, dim_worker, warp_per_block, _stream()))
+    return out
+
+
+def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts, part_size=0,
+                            blockx=4, blocky=16, out=None, deg_row=None, num_rows=None):
+    n = d_out.size(0) if num_rows is None else num_rows
+    dim = d_out.size(1)
+    ld = _row_stride(d_out, "d_out")
+    if out is None:
+        out = torch.empty(n, dim, device=d_out.device, dtype=torch.float32)
+    deg_row = degrees if deg_row is None else deg_row
+    check(lib().eppgcn_spmm_backward_compacted(
+        _dev(out, torch.float32, "d_in"), d_out.data_ptr(), ld,
+        _dev(ids, torch.int32, "ids"), _dev(part_ptr, torch.int32, "part_ptr"),
+        _dev(edge_list, torch.int32, "edge_list"),
+        _dev(deg_row, torch.float32, "deg_row"), _dev(degrees, torch.float32, "degrees"),
+        n, dim, int(num_parts), part_size, blockx, blocky, _stream()))
+    return out
+
+
+def mask_forward(ids, part_ptr, edge_list, src_mask, ngh_mask, back_edge_mask, node_degs,
+                 num_layers, layer, blockx=4, blocky=16, row_offset=0):
+    is_last = int(layer == num_layers)
+    ngh = None if (ngh_mask is None or ngh_mask.numel() == 0) else _dev(ngh_mask, torch.bool, "ngh_mask")
+    check(lib().eppgcn_mask_forward(
+        _dev(ids, torch.int32, "id"), _dev(part_ptr, torch.int32, "partPointer"),
+        _dev(edge_list, torch.int32, "edgeList"), _dev(src_mask, torch.bool, "src_mask"), ngh,
+        _dev(back_edge_mask, torch.int32, "backEdgeMask"), _dev(node_degs, torch.int32, "node_degs"),
+        ids.numel(), is_last, row_offset, blockx, blocky, _stream()))
+
+
+def _finish(counter: torch.Tensor) -> tuple[int, int]:
+    """Reads the (result, status) pair a scan entry point left on the device."""
+    vals = counter.cpu()          # synchronises with the producing stream
+    if int(vals[1]) != EPP_OK:
+        raise EppError(int(vals[1]), lib().eppgcn_status_string(int(vals[1])).decode())
+    return int(vals[0]), int(vals[1])
+
+
+def compact_mask(edge_mask, col_idx, mode=0):
+    """Returns ``(id[E], edge_list[E], valid_len)``; the trailing entries are zero."""
+    length = edge_mask.numel()
+    dev = edge_mask.device
+    out_id = torch.empty_like(edge_mask)
+    out_edge = torch.empty_like(col_idx)
+    nbytes = lib().eppgcn_compact_scratch_bytes(length)
+    scratch = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
+    counter = torch.empty(2, dtype=torch.int32, device=dev)
+    check(lib().eppgcn_compact_mask(
+        _dev(edge_mask, torch.int32, "edge_mask"), _dev(col_idx, torch.int32, "column_index"),
+        out_id.data_ptr(), out_edge.data_ptr(), length, scratch.data_ptr(), nbytes,
+        counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
+    valid, _ = _finish(counter)
+    return out_id, out_edge, valid
+
+
+def split_parts(node_deg, num_edges, part_size, mode=0):
+    """Returns ``(part_pointer[num_edges], num_parts)``."""
+    n = node_deg.numel()
+    dev = node_deg.device
+    out = torch.empty(num_edges, dtype=torch.int32, device=dev)
+    nbytes = lib().eppgcn_split_scratch_bytes(n)
+    scratch = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
+    counter = torch.empty(2, dtype=torch.int32, device=dev)
+    check(lib().eppgcn_split_parts(
+        _dev(node_deg, torch.int32, "node_deg"), n, int(part_size), out.data_ptr(), num_edges,
+        scratch.data_ptr(), nbytes, counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
+    parts, _ = _finish(counter)
+    return out, parts
+
+
+def count_nonzero(values) -> int:
+    counter = torch.empty(1, dtype=torch.int32, device=values.device)
+    check(lib().eppgcn_count_nonzero(_dev(values, torch.int32, "values"), values.numel(),
+                                     counter.data_ptr(), _stream()))
+    return int(counter.item())
+
+
+def build_part(part_size: int, indptr: torch.Tensor):
+    """Host partition; ``indptr`` is a CPU int32 tensor."""
+    if indptr.is_cuda or indptr.dtype != torch.int32:
+        raise RuntimeError("indptr must be a CPU int32 tensor")
+    indptr = indptr.contiguous()
+    n = indptr.numel() - 1
+    total = _LL(0)
+    check(lib().eppgcn_build_part_host(part_size, indptr.data_ptr(), n, None, None, C.byref(total)))
+    part_ptr = torch.empty(total.value + 1, dtype=torch.int32)
+    part2node = torch.empty(total.value, dtype=torch.int32)
+    check(lib().eppgcn_build_part_host(part_size, indptr.data_ptr(), n, part_ptr.data_ptr(),
+                                       part2node.data_ptr(), C.byref(total)))
+    return part_ptr, part2node
+
+
+def map_back_part_size(valid_node: int, valid_len: int) -> int:
+    v = _I(0)
+    check(lib().eppgcn_map_back_part_size(valid_node, valid_len, C.byref(v)))
+    return v.value
+
+
+def bucket_back_part_size(valid_node: int, valid_len: int) -> int:
+    v = _I(0)
+    check(lib().eppgcn_bucket_back_part_size(valid_node, valid_len, C.byref(v)))
+    return v.value
+
+
+def get_ginfo(node_deg: torch.Tensor, valid_len: int) -> torch.Tensor:
+    if node_deg.is_cuda or node_deg.dtype != torch.int32:
+        raise RuntimeError("node_deg must be a CPU int32 tensor")
+    node_deg = node_deg.contiguous()
+    out = torch.zeros(10, dtype=torch.float32)
+    check(lib().eppgcn_get_ginfo_host(node_deg.data_ptr(), node_deg.numel(), valid_len, out.data_ptr()))
+    return out
+
+
+def time_read() -> list[float]:
+    out = (C.c_float * 11)()
+    check(lib().eppgcn_time_read(out))
+    return list(out)

@@ -1,0 +1,352 @@
+// Python extension module "GNNAdvisor": the reference's operator API
+// (EPPGCN/GCNConv/EPPGCN.cpp:388-403) on top of the eppgcn_b200 C-ABI.
+//
+// Every function keeps the reference's name, positional arguments and return
+// shape.  Differences, all towards exactness or safety:
+//   * work is enqueued on torch's current stream and the per-epoch operators do
+//     not block the host (the reference synchronises after every kernel);
+//   * CUDA failures raise RuntimeError instead of calling exit();
+//   * build_part returns int32 tensors (the reference returns float32, exact
+//     only below 2^24; callers apply .int() either way) and always closes the
+//     last group (EPPGCN.cpp:222-223 skips that when the last vertex is empty);
+//   * compact_back_edge reports valid_len in a float64 tensor (float32 in the
+//     reference, EPPGCN.cpp:293-294);
+//   * split_back_part is exact for any degree (the reference handles at most
+//     1023 parts per vertex, cuCompactor.cu:500,527).
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <vector>
+
+#include "eppgcn_b200.h"
+
+namespace {
+
+#define CHECK_CUDA(x) TORCH_CHECK(x.is_cuda(), #x " must be a CUDA tensor")
+#define CHECK_CONTIGUOUS(x) TORCH_CHECK(x.is_contiguous(), #x " must be contiguous")
+#define CHECK_INPUT(x) CHECK_CUDA(x); CHECK_CONTIGUOUS(x)
+#define CHECK_I32(x) TORCH_CHECK(x.scalar_type() == at::kInt, #x " must be an int32 tensor")
+#define CHECK_F32(x) TORCH_CHECK(x.scalar_type() == at::kFloat, #x " must be a float32 tensor")
+#define CHECK_BOOL(x) TORCH_CHECK(x.scalar_type() == at::kBool, #x " must be a bool tensor")
+
+void epp_check(int status, const char *what) {
+  TORCH_CHECK(status == EPP_OK, what, " failed: ", eppgcn_status_string(status), ": ", eppgcn_last_error());
+}
+
+void *current_stream() { return static_cast<void *>(at::cuda::getCurrentCUDAStream().stream()); }
+
+// RAII pair of timer marks on the current stream.
+struct ScopedTime {
+  int slot, category, layer;
+  ScopedTime(int category_, int layer_ = 0) : slot(eppgcn_time_begin(current_stream())), category(category_), layer(layer_) {}
+  ~ScopedTime() { eppgcn_time_end(slot, category, layer, current_stream()); }
+};
+
+int padded_width(int64_t dim) { return static_cast<int>((dim + 7) / 8 * 8); }
+
+// X @ W written into rows whose stride is a multiple of 32 bytes, so every
+// gathered row starts on a sector boundary and can be fetched with 16-byte
+// loads whatever the output width (22 classes -> 24 floats).
+torch::Tensor update_padded(const torch::Tensor &x, const torch::Tensor &w) {
+  const int64_t n = x.size(0), d = w.size(1);
+  const int64_t ld = padded_width(d);
+  if (ld == d) return at::mm(x, w);
+  auto full = at::empty({n, ld}, x.options());
+  auto view = full.narrow(1, 0, d);
+  at::mm_out(view, x, w);
+  return view;
+}
+
+torch::Tensor aggregate_forward(const torch::Tensor &feat, const torch::Tensor &row_pointers,
+                                const torch::Tensor &column_index, const torch::Tensor &degrees,
+                                const torch::Tensor &part_pointers, const torch::Tensor &part2Node,
+                                int partSize, int dimWorker, int warpPerBlock) {
+  const int64_t n = feat.size(0), d = feat.size(1);
+  TORCH_CHECK(row_pointers.numel() == n + 1, "row_pointers must have num_nodes + 1 entries");
+  TORCH_CHECK(degrees.numel() >= n, "degrees must have one entry per vertex");
+  TORCH_CHECK(part_pointers.numel() == part2Node.numel() + 1 || part2Node.numel() == 0,
+              "part_pointers must have one more entry than part2Node");
+  auto out = at::empty({n, d}, feat.options());
+  const int64_t ld = n > 1 ? feat.stride(0) : std::max<int64_t>(feat.stride(0), d);
+  epp_check(eppgcn_spmm_forward(out.data_ptr<float>(), feat.data_ptr<float>(), ld,
+                                row_pointers.data_ptr<int>(), column_index.data_ptr<int>(),
+                                degrees.data_ptr<float>(), degrees.data_ptr<float>(),
+                                part_pointers.data_ptr<int>(), part2Node.data_ptr<int>(),
+                                static_cast<int>(n), static_cast<int>(d), static_cast<int>(part2Node.numel()),
+                                partSize, dimWorker, warpPerBlock, current_stream()),
+            "eppgcn_spmm_forward");
+  return out;
+}
+
+// forward(input, weight, row_pointers, column_index, degrees, part_pointers,
+//         part2Node, partSize, dimWorker, warpPerBlock) -> [output]
+// EPPGCN.cpp:79-102, EPPGCN_kernel.cu:123-202.
+std::vector<torch::Tensor> spmm_forward(torch::Tensor input, torch::Tensor weight, torch::Tensor row_pointers,
+                                        torch::Tensor column_index, torch::Tensor degrees,
+                                        torch::Tensor part_pointers, torch::Tensor part2Node, int partSize,
+                                        int dimWorker, int warpPerBlock) {
+  CHECK_INPUT(input); CHECK_INPUT(weight); CHECK_INPUT(row_pointers); CHECK_INPUT(column_index);
+  CHECK_INPUT(degrees); CHECK_INPUT(part_pointers); CHECK_INPUT(part2Node);
+  CHECK_F32(input); CHECK_F32(weight); CHECK_F32(degrees);
+  CHECK_I32(row_pointers); CHECK_I32(column_index); CHECK_I32(part_pointers); CHECK_I32(part2Node);
+  c10::cuda::CUDAGuard guard(input.device());
+  torch::Tensor tmp;
+  {
+    ScopedTime t(1);
+    tmp = update_padded(input, weight);
+  }
+  ScopedTime t(0);
+  return {aggregate_forward(tmp, row_pointers, column_index, degrees, part_pointers, part2Node, partSize,
+                            dimWorker, warpPerBlock)};
+}
+
+// backward(d_output, X, W, row_pointers, column_index, degrees, part_pointers,
+//          part2Node, partSize, dimWorker, warpPerBlock) -> [d_input, d_weight]
+// The uncompacted backward of EPPGCN.cpp:104-130, EPPGCN_kernel.cu:395-469.
+std::vector<torch::Tensor> spmm_backward(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
+                                         torch::Tensor row_pointers, torch::Tensor column_index,
+                                         torch::Tensor degrees, torch::Tensor part_pointers,
+                                         torch::Tensor part2Node, int partSize, int dimWorker,
+                                         int warpPerBlock) {
+  CHECK_INPUT(d_output); CHECK_INPUT(X); CHECK_INPUT(W); CHECK_INPUT(row_pointers); CHECK_INPUT(column_index);
+  CHECK_INPUT(degrees); CHECK_INPUT(part_pointers); CHECK_INPUT(part2Node);
+  CHECK_F32(d_output); CHECK_F32(X); CHECK_F32(W); CHECK_F32(degrees);
+  CHECK_I32(row_pointers); CHECK_I32(column_index); CHECK_I32(part_pointers); CHECK_I32(part2Node);
+  c10::cuda::CUDAGuard guard(d_output.device());
+  torch::Tensor d_input_prime;
+  {
+    ScopedTime t(2, 0);
+    d_input_prime = aggregate_forward(d_output, row_pointers, column_index, degrees, part_pointers, part2Node,
+                                      partSize, dimWorker, warpPerBlock);
+  }
+  ScopedTime t(3);
+  auto d_input = at::mm(d_input_prime, W.transpose(0, 1));
+  auto d_weight = at::mm(X.transpose(0, 1), d_input_prime);
+  return {d_input, d_weight};
+}
+
+// mask_forward(id, partPointer, edgeList, src_mask, ngh_mask, backEdgeMask,
+//              node_degs, num_layers, layer, blockx, blocky) -> None
+// EPPGCN.cpp:132-155, EPPGCN_kernel.cu:297-388.
+void mask_forward(torch::Tensor id, torch::Tensor partPointer, torch::Tensor edgeList, torch::Tensor src_mask,
+                  torch::Tensor ngh_mask, torch::Tensor backEdgeMask, torch::Tensor node_degs, int num_layers,
+                  int layer, int blockx, int blocky) {
+  CHECK_INPUT(id); CHECK_INPUT(partPointer); CHECK_INPUT(edgeList); CHECK_INPUT(src_mask);
+  CHECK_INPUT(ngh_mask); CHECK_INPUT(backEdgeMask); CHECK_INPUT(node_degs);
+  CHECK_I32(id); CHECK_I32(partPointer); CHECK_I32(edgeList); CHECK_I32(backEdgeMask); CHECK_I32(node_degs);
+  CHECK_BOOL(src_mask); CHECK_BOOL(ngh_mask);
+  const bool is_last = layer == num_layers;
+  TORCH_CHECK(is_last || ngh_mask.numel() == src_mask.numel(),
+              "ngh_mask must cover every vertex before the last preparation step");
+  TORCH_CHECK(partPointer.numel() == id.numel() + 1 || id.numel() == 0,
+              "partPointer must have one more entry than id");
+  c10::cuda::CUDAGuard guard(id.device());
+  ScopedTime t(4);
+  epp_check(eppgcn_mask_forward(id.data_ptr<int>(), partPointer.data_ptr<int>(), edgeList.data_ptr<int>(),
+                                reinterpret_cast<const unsigned char *>(src_mask.data_ptr<bool>()),
+                                ngh_mask.numel() ? reinterpret_cast<unsigned char *>(ngh_mask.data_ptr<bool>())
+                                                 : nullptr,
+                                backEdgeMask.data_ptr<int>(), node_degs.data_ptr<int>(),
+                                static_cast<int>(id.numel()), is_last ? 1 : 0, 0, blockx, blocky,
+                                current_stream()),
+            "eppgcn_mask_forward");
+}
+
+// ours_backward(d_output, X, W, id, partPointer, edgeList, degrees, partSize,
+//               numParts, layer, blockx, blocky) -> [d_input, d_weight]
+// EPPGCN.cpp:157-184, EPPGCN_kernel.cu:547-624.
+std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
+                                         torch::Tensor id, torch::Tensor partPointer, torch::Tensor edgeList,
+                                         torch::Tensor degrees, int partSize, int numParts, int layer,
+                                         int blockx, int blocky) {
+  CHECK_INPUT(d_output); CHECK_INPUT(X); CHECK_INPUT(W); CHECK_INPUT(id); CHECK_INPUT(partPointer);
+  CHECK_INPUT(edgeList); CHECK_INPUT(degrees);
+  CHECK_F32(d_output); CHECK_F32(X); CHECK_F32(W); CHECK_F32(degrees);
+  CHECK_I32(id); CHECK_I32(partPointer); CHECK_I32(edgeList);
+  TORCH_CHECK(numParts >= 0 && numParts < partPointer.numel() + (numParts == 0 ? 1 : 0),
+              "numParts exceeds the length of partPointer");
+  c10::cuda::CUDAGuard guard(d_output.device());
+  const int64_t n = d_output.size(0), d = d_output.size(1);
+  auto d_input_prime = at::empty({n, d}, d_output.options());
+  {
+    ScopedTime t(2, layer);
+    epp_check(eppgcn_spmm_backward_compacted(d_input_prime.data_ptr<float>(), d_output.data_ptr<float>(), d,
+                                             id.data_ptr<int>(), partPointer.data_ptr<int>(),
+                                             edgeList.data_ptr<int>(), degrees.data_ptr<float>(),
+                                             degrees.data_ptr<float>(), static_cast<int>(n), static_cast<int>(d),
+                                             numParts, partSize, blockx, blocky, current_stream()),
+              "eppgcn_spmm_backward_compacted");
+  }
+  ScopedTime t(3);
+  auto d_input = at::mm(d_input_prime, W.transpose(0, 1));
+  auto d_weight = at::mm(X.transpose(0, 1), d_input_prime);
+  return {d_input, d_weight};
+}
+
+// build_part(partSize, indptr) -> [partPtr, part2Node]      EPPGCN.cpp:186-227
+std::vector<torch::Tensor> build_part(int partSize, torch::Tensor indptr) {
+  TORCH_CHECK(!indptr.is_cuda(), "indptr must be a CPU tensor");
+  CHECK_I32(indptr);
+  TORCH_CHECK(indptr.dim() == 1 && indptr.numel() >= 1, "indptr must be a 1-D tensor of num_nodes + 1 entries");
+  auto ip = indptr.contiguous();
+  const int n = static_cast<int>(ip.numel() - 1);
+  long long total = 0;
+  epp_check(eppgcn_build_part_host(partSize, ip.data_ptr<int>(), n, nullptr, nullptr, &total),
+            "eppgcn_build_part_host");
+  auto opts = at::TensorOptions().dtype(at::kInt).device(at::kCPU);
+  auto partPtr = at::empty({total + 1}, opts);
+  auto part2Node = at::empty({total}, opts);
+  epp_check(eppgcn_build_part_host(partSize, ip.data_ptr<int>(), n, partPtr.data_ptr<int>(),
+                                   part2Node.data_ptr<int>(), &total),
+            "eppgcn_build_part_host");
+  return {partPtr, part2Node};
+}
+
+struct Compacted {
+  torch::Tensor id, edge_list;
+  int valid_len;
+};
+
+Compacted compact_edges(const torch::Tensor &edge_mask, const torch::Tensor &column_index) {
+  CHECK_INPUT(edge_mask); CHECK_INPUT(column_index);
+  CHECK_I32(edge_mask); CHECK_I32(column_index);
+  TORCH_CHECK(edge_mask.numel() == column_index.numel(), "edge_mask and column_index must have equal length");
+  TORCH_CHECK(edge_mask.numel() < (1LL << 31), "edge count exceeds int32");
+  c10::cuda::CUDAGuard guard(edge_mask.device());
+  const int length = static_cast<int>(edge_mask.numel());
+  auto id = at::empty_like(edge_mask);
+  auto edge_list = at::empty_like(column_index);
+  const size_t bytes = eppgcn_compact_scratch_bytes(length);
+  auto scratch = at::empty({static_cast<int64_t>(bytes)}, edge_mask.options().dtype(at::kByte));
+  auto counter = at::empty({2}, edge_mask.options());
+  epp_check(eppgcn_compact_mask(edge_mask.data_ptr<int>(), column_index.data_ptr<int>(), id.data_ptr<int>(),
+                                edge_list.data_ptr<int>(), length, scratch.data_ptr(), bytes,
+                                counter.data_ptr<int>(), counter.data_ptr<int>() + 1, 0, current_stream()),
+            "eppgcn_compact_mask");
+  auto host = counter.cpu();
+  if (host.data_ptr<int>()[1] == EPP_ERR_SCAN_TIMEOUT) {   // bounded wait ran out: redo without waiting
+    epp_check(eppgcn_compact_mask(edge_mask.data_ptr<int>(), column_index.data_ptr<int>(), id.data_ptr<int>(),
+                                  edge_list.data_ptr<int>(), length, scratch.data_ptr(), bytes,
+                                  counter.data_ptr<int>(), counter.data_ptr<int>() + 1, 1, current_stream()),
+              "eppgcn_compact_mask");
+    host = counter.cpu();
+  }
+  epp_check(host.data_ptr<int>()[1], "eppgcn_compact_mask");
+  return {id, edge_list, host.data_ptr<int>()[0]};
+}
+
+struct Split {
+  torch::Tensor part_pointer;
+  int num_parts;
+};
+
+Split split_parts(const torch::Tensor &node_deg, int num_edges, int back_part_size) {
+  CHECK_INPUT(node_deg);
+  CHECK_I32(node_deg);
+  TORCH_CHECK(num_edges >= 0, "num_edges must be non-negative");
+  TORCH_CHECK(back_part_size >= 1, "back_part_size must be >= 1, got ", back_part_size);
+  c10::cuda::CUDAGuard guard(node_deg.device());
+  const int n = static_cast<int>(node_deg.numel());
+  auto part_pointer = at::empty({num_edges}, node_deg.options());
+  const size_t bytes = eppgcn_split_scratch_bytes(n);
+  auto scratch = at::empty({static_cast<int64_t>(bytes)}, node_deg.options().dtype(at::kByte));
+  auto counter = at::empty({2}, node_deg.options());
+  for (int mode = 0; mode < 2; ++mode) {
+    epp_check(eppgcn_split_parts(node_deg.data_ptr<int>(), n, back_part_size,
+                                 num_edges ? part_pointer.data_ptr<int>() : nullptr, num_edges,
+                                 scratch.data_ptr(), bytes, counter.data_ptr<int>(), counter.data_ptr<int>() + 1,
+                                 mode, current_stream()),
+              "eppgcn_split_parts");
+    auto host = counter.cpu();
+    if (host.data_ptr<int>()[1] == EPP_OK) return {part_pointer, host.data_ptr<int>()[0]};
+    if (mode == 1) epp_check(host.data_ptr<int>()[1], "eppgcn_split_parts");
+  }
+  return {part_pointer, 0};
+}
+
+int count_active(const torch::Tensor &node_deg) {
+  CHECK_INPUT(node_deg);
+  CHECK_I32(node_deg);
+  c10::cuda::CUDAGuard guard(node_deg.device());
+  auto counter = at::empty({1}, node_deg.options());
+  epp_check(eppgcn_count_nonzero(node_deg.data_ptr<int>(), static_cast<int>(node_deg.numel()),
+                                 counter.data_ptr<int>(), current_stream()),
+            "eppgcn_count_nonzero");
+  return counter.item<int>();
+}
+
+// compact_back_edge(edge_mask, column_index) -> [id, edge_list, info]   EPPGCN.cpp:282-296
+std::vector<torch::Tensor> compact_back_edge(torch::Tensor edge_mask, torch::Tensor column_index) {
+  Compacted c = compact_edges(edge_mask, column_index);
+  auto info = at::zeros({1}, at::TensorOptions().dtype(at::kDouble));
+  info.data_ptr<double>()[0] = c.valid_len;
+  return {c.id, c.edge_list, info};
+}
+
+// get_map_back_part_size(node_deg, valid_len) -> int   EPPGCN.cpp:298-325
+// Unclamped, as in the reference: the value can be zero or negative on large
+// graphs and the caller has to clamp it before split_back_part.
+int get_map_back_part_size(torch::Tensor node_deg, int valid_len) {
+  int ps = 0;
+  epp_check(eppgcn_map_back_part_size(count_active(node_deg), valid_len, &ps), "eppgcn_map_back_part_size");
+  return ps;
+}
+
+// split_back_part(node_deg, num_edges, back_part_size) -> [part_pointer, info]   EPPGCN.cpp:327-346
+std::vector<torch::Tensor> split_back_part(torch::Tensor node_deg, int num_edges, int back_part_size) {
+  Split s = split_parts(node_deg, num_edges, back_part_size);
+  auto info = at::zeros({1}, at::TensorOptions().dtype(at::kInt));
+  info.data_ptr<int>()[0] = s.num_parts;
+  return {s.part_pointer, info};
+}
+
+// build_back_part(edge_mask, column_index, node_deg, back_part_size, dim)
+//   -> [id, edge_list, part_pointer, info(float[2]) = {part size, num_parts}]   EPPGCN.cpp:229-280
+std::vector<torch::Tensor> build_back_part(torch::Tensor edge_mask, torch::Tensor column_index,
+                                           torch::Tensor node_deg, int back_part_size, int dim) {
+  (void)dim;
+  Compacted c = compact_edges(edge_mask, column_index);
+  if (back_part_size == 0) {
+    epp_check(eppgcn_bucket_back_part_size(count_active(node_deg), c.valid_len, &back_part_size),
+              "eppgcn_bucket_back_part_size");
+    TORCH_CHECK(back_part_size >= 1, "average active degree is 512 or more: pass an explicit back_part_size");
+  }
+  Split s = split_parts(node_deg, static_cast<int>(column_index.numel()), back_part_size);
+  auto info = at::zeros({2}, at::TensorOptions().dtype(at::kDouble));
+  info.data_ptr<double>()[0] = back_part_size;
+  info.data_ptr<double>()[1] = s.num_parts;
+  return {c.id, c.edge_list, s.part_pointer, info};
+}
+
+// get_ginfo(node_deg, valid_len) -> float32[10]   EPPGCN.cpp:348-386
+torch::Tensor get_ginfo(torch::Tensor node_deg, int valid_len) {
+  TORCH_CHECK(!node_deg.is_cuda(), "node_deg must be a CPU tensor");
+  CHECK_I32(node_deg);
+  auto nd = node_deg.contiguous();
+  auto re = at::zeros({10}, at::TensorOptions().dtype(at::kFloat));
+  epp_check(eppgcn_get_ginfo_host(nd.data_ptr<int>(), static_cast<int>(nd.numel()), valid_len,
+                                  re.data_ptr<float>()),
+            "eppgcn_get_ginfo_host");
+  return re;
+}
+
+void print_time() { epp_check(eppgcn_print_time(), "eppgcn_print_time"); }
+void clear_time() { epp_check(eppgcn_clear_time(), "eppgcn_clear_time"); }
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("forward", &spmm_forward, "GCN layer forward: X @ W, then neighbour-group aggregation (CUDA)");
+  m.def("backward", &spmm_backward, "GCN layer backward over the whole graph (CUDA)");
+  m.def("mask_forward", &mask_forward, "execution-path marking for one preparation step (CUDA)");
+  m.def("ours_backward", &ours_backward, "GCN layer backward over the prepared execution path (CUDA)");
+  m.def("print_time", &print_time, "print accumulated kernel times");
+  m.def("clear_time", &clear_time, "reset accumulated kernel times");
+  m.def("build_part", &build_part, "neighbour-group partition (CPU)");
+  m.def("build_back_part", &build_back_part, "compaction + part-size rule + splitting in one call (CUDA)");
+  m.def("compact_back_edge", &compact_back_edge, "stable compaction of the marked edges (CUDA)");
+  m.def("get_map_back_part_size", &get_map_back_part_size, "regression rule for the backward part size (CUDA)");
+  m.def("split_back_part", &split_back_part, "split active rows into backward parts (CUDA)");
+  m.def("get_ginfo", &get_ginfo, "degree histogram features (CPU)");
+}

@@ -1,0 +1,190 @@
+/*
+ * eppgcn_b200 -- C ABI of the B200 (sm_100a) GCN aggregation hot path.
+ *
+ * Every entry point is `extern "C"`, takes plain pointers and sizes, returns
+ * an int status (0 = EPP_OK) and never terminates the process.  Device
+ * pointers are raw CUDA pointers on the current device; `stream` is a
+ * `cudaStream_t` passed as `void*` (NULL = legacy default stream).  Device
+ * entry points only enqueue work: they do not synchronise and they allocate
+ * nothing (scratch is supplied by the caller) unless the comment says
+ * otherwise.  Inputs are borrowed and never written unless marked in/out.
+ *
+ * Each declaration names the interface of the reference project
+ * (Catriminal/EPPGCN, paths inside that project) that it stands in for.
+ */
+#ifndef EPPGCN_B200_H_
+#define EPPGCN_B200_H_
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  EPP_OK = 0,
+  EPP_ERR_BAD_ARG = 1,       /* null pointer, negative size, part size < 1 ...      */
+  EPP_ERR_CUDA = 2,          /* a CUDA runtime call or launch failed                  */
+  EPP_ERR_SCAN_TIMEOUT = 3,  /* the bounded look-back wait of a scan kernel ran out  */
+  EPP_ERR_TOO_LARGE = 4      /* a size is beyond what the entry point supports       */
+};
+
+/* Library version as major*10000 + minor*100 + patch. */
+int eppgcn_version(void);
+/* Static name of a status code. */
+const char *eppgcn_status_string(int status);
+/* Message of the calling thread's most recent failure ("" if none). */
+const char *eppgcn_last_error(void);
+
+/* ------------------------------------------------------------------------
+ * Forward neighbour-group aggregation.
+ * Replaces spmm_forward_cuda_kernel and its launch
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:150-184, :204-295), and, applied to
+ * d_output, spmm_backward_cuda_kernel (:415-442, :471-545).
+ *
+ *   out[r][:] = sum over edges e of row r:
+ *               (deg_row[r] * deg_col[col_idx[e]]) * feat[col_idx[e]][:]
+ *
+ * out       [num_nodes][dim] dense fp32, fully overwritten (rows without
+ *           edges come back zero).
+ * feat      fp32 rows with a stride of feat_ld floats (feat_ld >= dim).
+ * row_ptr   [num_nodes+1], col_idx [row_ptr[num_nodes]]  int32 CSR.
+ * deg_row / deg_col   per-vertex factors of the destination and the source
+ *           side.  The reference passes one `degrees` array for both; a
+ *           row-partitioned caller passes `degrees + first_row` as deg_row.
+ * part_ptr  [num_parts+1], part2node [num_parts]: the neighbour groups of
+ *           build_part -- consecutive, non-overlapping, covering every row.
+ * part_size, dim_worker, warp_per_block: the reference's launch knobs
+ *           (EPPGCN/param.py:80-124).  Accepted for signature parity; the
+ *           result does not depend on them.
+ */
+int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
+                        const int *row_ptr, const int *col_idx,
+                        const float *deg_row, const float *deg_col,
+                        const int *part_ptr, const int *part2node,
+                        int num_nodes, int dim, int num_parts,
+                        int part_size, int dim_worker, int warp_per_block,
+                        void *stream);
+
+/* ------------------------------------------------------------------------
+ * Backward aggregation over the prepared execution path.
+ * Replaces ours_backward_cuda_kernel and its launch
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:562-589, :626-670).
+ *
+ *   d_in[r][:] = sum over compacted edges e with ids[e] == r:
+ *                (deg_row[r] * deg_col[edge_list[e]]) * d_out[edge_list[e]][:]
+ *
+ * d_in      [num_nodes][dim] dense fp32, fully overwritten (rows off the
+ *           path come back zero).
+ * ids, edge_list   outputs of eppgcn_compact_mask (valid prefix).
+ * part_ptr  [num_parts+1] output of eppgcn_split_parts; part p covers
+ *           compacted edges [part_ptr[p], part_ptr[p+1]) of one row.
+ * part_size, blockx, blocky: reference knobs (EPPGCN/param.py:6-24,182-200),
+ *           accepted for parity; the result does not depend on them.
+ */
+int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
+                                   const int *ids, const int *part_ptr, const int *edge_list,
+                                   const float *deg_row, const float *deg_col,
+                                   int num_nodes, int dim, int num_parts,
+                                   int part_size, int blockx, int blocky,
+                                   void *stream);
+
+/* ------------------------------------------------------------------------
+ * Execution-path marking for one preparation step.
+ * Replaces mask_forward_cuda_kernel and its launch
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:311-333, :351-388).
+ *
+ * For every edge e of group p (row r = ids[p], column c = edge_list[e]):
+ *   if (!is_last && src_mask[r + row_offset])  ngh_mask[r + row_offset] = ngh_mask[c] = 1
+ *   if (src_mask[c])                           back_edge_mask[e] = r, node_degs[r] += 1
+ * src_mask / ngh_mask are byte masks (torch.bool).  ngh_mask may be NULL when
+ * is_last.  back_edge_mask (expected -1) and node_degs (expected 0) are
+ * updated in place.  row_offset is 0 for the reference's call; a
+ * row-partitioned caller passes the global id of its first row.
+ */
+int eppgcn_mask_forward(const int *ids, const int *part_ptr, const int *edge_list,
+                        const unsigned char *src_mask, unsigned char *ngh_mask,
+                        int *back_edge_mask, int *node_degs,
+                        int num_parts, int is_last, int row_offset,
+                        int blockx, int blocky, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Stable compaction of the marked edges.
+ * Replaces compact_mask -> cuCompactor_mask::compact
+ * (EPPGCN/GCNConv/cuCompactor.cu:344-463, :682-686).
+ *
+ * Keeps, in order, every e with edge_mask[e] != -1:
+ *   out_id[k] = edge_mask[e], out_edge[k] = col_idx[e]
+ * and zero-fills both outputs from the kept count up to `length`.  The kept
+ * count is stored to *valid_len_dev (device int).  `scratch` must hold
+ * eppgcn_compact_scratch_bytes(length) bytes; the call clears what it needs.
+ * `status_dev` (device int, may alias nothing else) receives EPP_OK or
+ * EPP_ERR_SCAN_TIMEOUT when the kernels finish.
+ * mode 0: one pass with a decoupled look-back scan (bounded wait);
+ * mode 1: three kernels (tile counts, scan of counts, scatter), no waiting.
+ */
+size_t eppgcn_compact_scratch_bytes(int length);
+int eppgcn_compact_mask(const int *edge_mask, const int *col_idx,
+                        int *out_id, int *out_edge, int length,
+                        void *scratch, size_t scratch_bytes,
+                        int *valid_len_dev, int *status_dev, int mode, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Splitting the active rows into backward parts.
+ * Replaces compact_part -> cuCompactor_part::compact followed by
+ * exclusive_scan (EPPGCN/GCNConv/cuCompactor.cu:492-619, :42-48, :688-692).
+ *
+ * For every vertex v in order with node_deg[v] > 0, ceil(deg/part_size)
+ * parts; part_pointer[j] is the compacted-edge offset where part j starts and
+ * part_pointer[num_parts] the total.  Entries past num_parts (up to out_len)
+ * are zeroed; an entry that would land at index out_len is dropped.
+ * *num_parts_dev receives the part count.  Exact for any int32 input (the
+ * reference is limited to 1023 parts per vertex).  scratch/status/mode as for
+ * eppgcn_compact_mask, sized by eppgcn_split_scratch_bytes(num_nodes).
+ */
+size_t eppgcn_split_scratch_bytes(int num_nodes);
+int eppgcn_split_parts(const int *node_deg, int num_nodes, int part_size,
+                       int *part_pointer, int out_len,
+                       void *scratch, size_t scratch_bytes,
+                       int *num_parts_dev, int *status_dev, int mode, void *stream);
+
+/* Number of non-zero entries, stored to *count_dev.
+ * Replaces compact_count (EPPGCN/GCNConv/cuCompactor.cu:638-678, :694-696). */
+int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Host-side helpers (CPU pointers, synchronous).
+ */
+/* Neighbour-group partition, replaces build_part
+ * (EPPGCN/GCNConv/EPPGCN.cpp:186-227).  Call with part_ptr == NULL to get
+ * only *num_parts, then with part_ptr[num_parts+1], part2node[num_parts].
+ * part_ptr[num_parts] is always indptr[num_nodes]. */
+int eppgcn_build_part_host(int part_size, const int *indptr, int num_nodes,
+                           int *part_ptr, int *part2node, long long *num_parts);
+/* Regression rule of get_map_back_part_size (EPPGCN.cpp:304-310), unclamped. */
+int eppgcn_map_back_part_size(int valid_node, int valid_len, int *part_size);
+/* Degree-bucket rule of build_back_part (EPPGCN.cpp:243-258); leaves 0 for
+ * an average degree of 512 or more, as the reference does. */
+int eppgcn_bucket_back_part_size(int valid_node, int valid_len, int *part_size);
+/* Ten degree-histogram features, replaces get_ginfo (EPPGCN.cpp:348-386). */
+int eppgcn_get_ginfo_host(const int *node_deg, int num_nodes, int valid_len, float *out10);
+
+/* ------------------------------------------------------------------------
+ * Timers behind print_time / clear_time
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:89-116).  Events are recorded on the
+ * caller's stream and resolved lazily, so timing adds no host stall per op.
+ * Categories: 0 forward aggregation, 1 forward update (GEMM),
+ * 2 backward aggregation (with 1-based layer), 3 backward update, 4 mask.
+ */
+int eppgcn_timing_enable(int on);                 /* returns previous state */
+int eppgcn_time_begin(void *stream);              /* slot handle, or -1 when off */
+int eppgcn_time_end(int slot, int category, int layer, void *stream);
+/* Accumulated milliseconds: out[0..4] by category, out[5..10] per-layer backward aggregation. */
+int eppgcn_time_read(float *out11);
+int eppgcn_print_time(void);                      /* same keys and format as the reference */
+int eppgcn_clear_time(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EPPGCN_B200_H_ */

@@ -167,16 +167,18 @@ def compact_mask(edge_mask, col_idx, mode=0):
     return out_id, out_edge, valid
 
 
-def split_parts(node_deg, num_edges, part_size, mode=0):
-    """Returns ``(part_pointer[num_edges], num_parts)``."""
+def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):
+    """Returns ``(part_pointer[out_len], num_parts)``; ``out_len`` defaults to
+    ``num_edges + 1`` so the closing pointer always fits."""
     n = node_deg.numel()
     dev = node_deg.device
-    out = torch.empty(num_edges, dtype=torch.int32, device=dev)
+    out_len = num_edges + 1 if out_len is None else out_len
+    out = torch.empty(out_len, dtype=torch.int32, device=dev)
     nbytes = lib().eppgcn_split_scratch_bytes(n)
     scratch = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
     counter = torch.empty(2, dtype=torch.int32, device=dev)
     check(lib().eppgcn_split_parts(
-        _dev(node_deg, torch.int32, "node_deg"), n, int(part_size), out.data_ptr(), num_edges,
+        _dev(node_deg, torch.int32, "node_deg"), n, int(part_size), out.data_ptr(), out_len,
         scratch.data_ptr(), nbytes, counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
     parts, _ = _finish(counter)
     return out, parts

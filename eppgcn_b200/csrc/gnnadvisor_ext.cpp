@@ -12,7 +12,8 @@
 //   * compact_back_edge reports valid_len in a float64 tensor (float32 in the
 //     reference, EPPGCN.cpp:293-294);
 //   * split_back_part is exact for any degree (the reference handles at most
-//     1023 parts per vertex, cuCompactor.cu:500,527).
+//     1023 parts per vertex, cuCompactor.cu:500,527) and returns num_edges + 1
+//     entries, one more than the reference, so the closing pointer always fits.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
@@ -164,8 +165,8 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
   CHECK_INPUT(edgeList); CHECK_INPUT(degrees);
   CHECK_F32(d_output); CHECK_F32(X); CHECK_F32(W); CHECK_F32(degrees);
   CHECK_I32(id); CHECK_I32(partPointer); CHECK_I32(edgeList);
-  TORCH_CHECK(numParts >= 0 && numParts < partPointer.numel() + (numParts == 0 ? 1 : 0),
-              "numParts exceeds the length of partPointer");
+  TORCH_CHECK(numParts >= 0 && (numParts == 0 || numParts < partPointer.numel()),
+              "partPointer must hold numParts + 1 entries");
   c10::cuda::CUDAGuard guard(d_output.device());
   const int64_t n = d_output.size(0), d = d_output.size(1);
   auto d_input_prime = at::empty({n, d}, d_output.options());
@@ -248,13 +249,16 @@ Split split_parts(const torch::Tensor &node_deg, int num_edges, int back_part_si
   TORCH_CHECK(back_part_size >= 1, "back_part_size must be >= 1, got ", back_part_size);
   c10::cuda::CUDAGuard guard(node_deg.device());
   const int n = static_cast<int>(node_deg.numel());
-  auto part_pointer = at::empty({num_edges}, node_deg.options());
+  // One entry more than the reference allocates (EPPGCN.cpp:335-336), so the
+  // closing pointer exists even when every part holds a single edge.
+  const int out_len = num_edges + 1;
+  auto part_pointer = at::empty({out_len}, node_deg.options());
   const size_t bytes = eppgcn_split_scratch_bytes(n);
   auto scratch = at::empty({static_cast<int64_t>(bytes)}, node_deg.options().dtype(at::kByte));
   auto counter = at::empty({2}, node_deg.options());
   for (int mode = 0; mode < 2; ++mode) {
     epp_check(eppgcn_split_parts(node_deg.data_ptr<int>(), n, back_part_size,
-                                 num_edges ? part_pointer.data_ptr<int>() : nullptr, num_edges,
+                                 part_pointer.data_ptr<int>(), out_len,
                                  scratch.data_ptr(), bytes, counter.data_ptr<int>(), counter.data_ptr<int>() + 1,
                                  mode, current_stream()),
               "eppgcn_split_parts");

@@ -164,8 +164,9 @@ def compact_back_edge_loops(edge_mask, column_index):
 # --------------------------------------------------------------------------
 # splitting active rows into parts   cuCompactor.cu:514-619, :42-48, EPPGCN.cpp:327-346
 # --------------------------------------------------------------------------
-def split_back_part(node_deg, num_edges: int, part_size: int):
-    """``(part_pointer[num_edges], num_parts)``.  Every vertex with
+def split_back_part(node_deg, num_edges: int, part_size: int, out_len: int | None = None):
+    """``(part_pointer[out_len], num_parts)``; ``out_len`` defaults to the
+    reference's ``num_edges`` (EPPGCN.cpp:335-336).  Every vertex with
     ``node_deg > 0`` contributes, in vertex order, ``ceil(deg/part_size)``
     part sizes ``part_size, ..., part_size, remainder`` (cuCompactor.cu:566-572);
     ``part_pointer`` is the exclusive scan of those sizes over
@@ -174,9 +175,11 @@ def split_back_part(node_deg, num_edges: int, part_size: int):
     The reference counts parts per vertex in 10 bits and per warp in 11 bits
     (cuCompactor.cu:500,527,549); :func:`split_reference_valid` tells whether
     an input lies inside that range.  This function is exact for any int32
-    input.  An entry that would fall at index ``num_edges`` (possible only
-    when ``num_parts == num_edges``) is dropped instead of written out of
-    bounds.
+    input.  An entry that would fall at index ``out_len`` (with the
+    reference's length: only when ``num_parts == num_edges``, where the
+    reference writes one element past its buffer) is dropped; the operator
+    module of this repository allocates ``num_edges + 1`` entries so the closing
+    pointer always exists.
     """
     if part_size < 1:
         raise ValueError("back part size must be >= 1")
@@ -193,8 +196,9 @@ def split_back_part(node_deg, num_edges: int, part_size: int):
     full = np.zeros(num_parts + 1, dtype=np.int64)
     full[:num_parts] = edge0[owner] + k * part_size
     full[num_parts] = edge0[-1]
-    out = np.zeros(num_edges, dtype=np.int32)
-    m = min(num_parts + 1, num_edges)
+    out_len = num_edges if out_len is None else out_len
+    out = np.zeros(out_len, dtype=np.int32)
+    m = min(num_parts + 1, out_len)
     out[:m] = full[:m]
     return out, num_parts
 
@@ -378,7 +382,7 @@ def prepare_execution_path(indptr, indices, train_mask, num_layers: int, part_si
     out = []
     for i in range(num_layers):
         ids, cols, valid = compact_back_edge(edge_masks[i], indices)
-        pp, nparts = split_back_part(node_degs[i], e, back_sizes[i])
+        pp, nparts = split_back_part(node_degs[i], e, back_sizes[i], out_len=e + 1)
         out.append(dict(id=ids, edgeList=cols, valid_len=valid, partPointer=pp,
                         numParts=nparts, partSize=back_sizes[i], node_degs=node_degs[i],
                         edge_mask=edge_masks[i]))

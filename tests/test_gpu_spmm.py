@@ -1,0 +1,129 @@
+"""CUDA aggregations through the C-ABI against the float64 oracle.
+Tolerance: |got - want| <= 1e-6 + 1e-5*|want| (atomics reorder the sums)."""
+import numpy as np
+import pytest
+import torch
+
+from eppgcn_b200 import capi
+from oracle import epp_oracle as O
+from tests.helpers import assert_close, degrees_of, random_csr, t
+
+pytestmark = pytest.mark.gpu
+
+GRAPHS = {
+    "tiny":   dict(n=9, avg_deg=2.0, seed=1, empty_frac=0.3),
+    "sparse": dict(n=300, avg_deg=3.0, seed=2, empty_frac=0.2),
+    "hubs":   dict(n=700, avg_deg=6.0, seed=3, hubs=3, hub_deg=650),
+    "dense":  dict(n=128, avg_deg=40.0, seed=4),
+}
+
+
+def run_forward(cuda, indptr, indices, dim, part_size, pad=0, seed=0, deg_kind="rsqrt"):
+    n = len(indptr) - 1
+    rng = np.random.Generator(np.random.PCG64(seed))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    deg = degrees_of(indptr, deg_kind)
+    pp, p2n = O.build_part(part_size, indptr)
+    full = torch.full((n, dim + pad), float("nan"), device=cuda)     # padding must never leak into the result
+    full[:, :dim] = t(feat, cuda)
+    out = capi.spmm_forward(full[:, :dim], t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda),
+                            t(p2n, cuda), part_size)
+    torch.cuda.synchronize()
+    return out.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat)
+
+
+@pytest.mark.parametrize("graph", sorted(GRAPHS))
+@pytest.mark.parametrize("dim", [1, 2, 3, 4, 5, 8, 16, 22, 32, 33, 64, 96, 128, 130, 200])
+def test_forward_dims(cuda, graph, dim):
+    indptr, indices = random_csr(**GRAPHS[graph])
+    got, want = run_forward(cuda, indptr, indices, dim, part_size=4)
+    assert_close(got, want, what=f"forward {graph} dim {dim}")
+
+
+@pytest.mark.parametrize("part_size", [1, 2, 7, 17, 32, 1000])
+@pytest.mark.parametrize("dim", [16, 22, 128])
+def test_forward_group_sizes(cuda, part_size, dim):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    got, want = run_forward(cuda, indptr, indices, dim, part_size)
+    assert_close(got, want, what=f"forward part_size {part_size} dim {dim}")
+
+
+@pytest.mark.parametrize("dim,pad", [(22, 2), (22, 10), (16, 8), (5, 3), (7, 1), (3, 1), (130, 6)])
+def test_forward_padded_row_stride(cuda, dim, pad):
+    indptr, indices = random_csr(**GRAPHS["sparse"])
+    got, want = run_forward(cuda, indptr, indices, dim, 5, pad=pad)
+    assert np.isfinite(got).all()
+    assert_close(got, want, what=f"forward dim {dim} stride {dim + pad}")
+
+
+def test_forward_reference_degree_convention(cuda):
+    """The operator multiplies whatever `degrees` holds; the reference loader
+    stores sqrt(deg) (EPPGCN/dataset.py:118-119)."""
+    indptr, indices = random_csr(**GRAPHS["sparse"])
+    got, want = run_forward(cuda, indptr, indices, 16, 3, deg_kind="sqrt")
+    assert_close(got, want, what="sqrt degrees")
+
+
+def test_forward_empty_graph_and_overwrite(cuda):
+    n, dim = 50, 16
+    indptr = np.zeros(n + 1, dtype=np.int32)
+    out = torch.full((n, dim), 7.0, device=cuda)
+    z = torch.zeros(0, dtype=torch.int32, device=cuda)
+    capi.spmm_forward(torch.ones(n, dim, device=cuda), t(indptr, cuda), z, torch.ones(n, device=cuda),
+                      torch.zeros(1, dtype=torch.int32, device=cuda), z, 4, out=out)
+    assert torch.count_nonzero(out).item() == 0, "rows without edges must come back zero"
+
+
+def test_forward_is_linear_and_repeatable(cuda):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    pp, p2n = O.build_part(8, indptr)
+    args = [t(a, cuda) for a in (indptr, indices, deg, pp, p2n)]
+    g = torch.Generator(device=cuda).manual_seed(1)
+    a = torch.randn(n, 32, device=cuda, generator=g)
+    b = torch.randn(n, 32, device=cuda, generator=g)
+    fa, fb, fab = (capi.spmm_forward(x, *args, 8) for x in (a, b, 2 * a - 3 * b))
+    torch.testing.assert_close(fab, 2 * fa - 3 * fb, rtol=1e-4, atol=1e-5)
+    again = capi.spmm_forward(a, *args, 8)
+    torch.testing.assert_close(again, fa, rtol=1e-5, atol=1e-6)
+
+
+def make_path(indptr, indices, ratio, layers, part_size, back_size, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    train = rng.random(len(indptr) - 1) < ratio
+    path, _ = O.prepare_execution_path(indptr, indices, train, layers, part_size, [back_size] * layers)
+    return path
+
+
+@pytest.mark.parametrize("dim", [1, 3, 4, 16, 22, 32, 64, 128, 150])
+@pytest.mark.parametrize("back_size", [1, 4, 32])
+def test_backward_compacted(cuda, dim, back_size):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    d_out = rng.standard_normal((n, dim)).astype(np.float32)
+    for conv in make_path(indptr, indices, 0.15, 2, 6, back_size, seed=dim):
+        got = capi.spmm_backward_compacted(t(d_out, cuda), t(conv["id"], cuda), t(conv["partPointer"], cuda),
+                                           t(conv["edgeList"], cuda), t(deg, cuda), conv["numParts"], back_size)
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, d_out,
+                                         conv["numParts"])
+        assert_close(got.cpu().numpy(), want, what=f"backward dim {dim} size {back_size}")
+
+
+@pytest.mark.parametrize("ratio", [0.0, 0.01, 0.5, 1.0])
+def test_backward_train_ratios(cuda, ratio):
+    indptr, indices = random_csr(**GRAPHS["sparse"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    d_out = np.random.Generator(np.random.PCG64(9)).standard_normal((n, 16)).astype(np.float32)
+    for conv in make_path(indptr, indices, ratio, 3, 4, 8, seed=11):
+        out = torch.full((n, 16), 5.0, device=cuda)
+        capi.spmm_backward_compacted(t(d_out, cuda), t(conv["id"], cuda), t(conv["partPointer"], cuda),
+                                     t(conv["edgeList"], cuda), t(deg, cuda), conv["numParts"], 8, out=out)
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, d_out,
+                                         conv["numParts"])
+        assert_close(out.cpu().numpy(), want, what=f"backward ratio {ratio}")
+        off_path = conv["node_degs"] == 0
+        assert np.all(out.cpu().numpy()[off_path] == 0), "rows off the path must come back zero"

@@ -11,10 +11,15 @@
 // with a segmented shuffle reduction, and only the head of each run touches
 // memory: a plain vector store when the run covers the whole row, a vector
 // atomic add otherwise (a row split across warps).
+#include <stdlib.h>
+#include <string.h>
+
 #include "common.cuh"
 
 namespace epp {
 namespace {
+
+inline bool aligned(const void *p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
 template <int VEC> struct VecT;
 template <> struct VecT<4> { using type = float4; };
@@ -187,6 +192,248 @@ __global__ void __launch_bounds__(256) group_spmm_kernel(const GroupArgs a) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Staged, persistent variant.
+//
+// A warp walks over "sets" of G = 32/LPR consecutive groups.  The column ids of
+// a set are one contiguous slice of the edge array; the warp copies that slice
+// into its private shared-memory slab with cp.async while it is still busy with
+// the previous set (two slabs per warp), and the group descriptors of the set
+// after that are already on their way in registers.  Inside a set the only
+// exposed memory latency is therefore the gather itself: every lane keeps
+// eight neighbour rows in flight, reads the column id as a shared-memory
+// broadcast and the source-side degree as a (sub-warp uniform) cached load.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async_4(int *smem_dst, const int *gmem_src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(int *smem_dst, const int *gmem_src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+struct SetMeta {
+  int beg, end, row;   // this sub-warp's group: edge range and destination row (-1: nothing to do)
+  int lo, hi;          // forward: row_ptr[row], row_ptr[row+1]; backward: row id of the edge before / after
+};
+
+template <bool BWD>
+__device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, long long set, long long nsets, int groups,
+                                                 int sub, int total_edges) {
+  SetMeta m{0, 0, -1, -1, -1};
+  const long long g = set * groups + sub;
+  if (set < nsets && g < a.num_parts) {
+    m.beg = __ldg(a.part_ptr + g);
+    m.end = __ldg(a.part_ptr + g + 1);
+    if (m.end > m.beg) {
+      if (BWD) {
+        m.row = __ldg(a.row_of + m.beg);
+        m.lo = m.beg > 0 ? __ldg(a.row_of + m.beg - 1) : -1;
+        m.hi = m.end < total_edges ? __ldg(a.row_of + m.end) : -1;
+      } else {
+        m.row = __ldg(a.row_of + g);
+        m.lo = __ldg(a.row_ptr + m.row);
+        m.hi = __ldg(a.row_ptr + m.row + 1);
+      }
+    } else {
+      m.end = m.beg;
+    }
+  }
+  return m;
+}
+
+template <int VEC, int LPR, bool BWD>
+__global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, const int slab, const int col_aligned) {
+  constexpr int G = kWarp / LPR;
+  constexpr int U = 8;
+  extern __shared__ __align__(16) int s_cols[];
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / LPR;
+  const int sl = lane % LPR;
+  const int wib = threadIdx.x >> 5;
+  const int wpb = blockDim.x >> 5;
+  int *const slab0 = s_cols + (wib * 2) * slab;   // this warp's two slabs: slab0 + cur * slab
+  const long long nsets = (static_cast<long long>(a.num_parts) + G - 1) / G;
+  const long long stride = static_cast<long long>(gridDim.x) * wpb;
+  long long set = static_cast<long long>(blockIdx.x) * wpb + wib;
+  if (set >= nsets) return;
+  const int total_edges = __ldg(a.part_ptr + a.num_parts);
+
+  // Starts the copy of one set's column ids; returns the first edge held by the
+  // slab, or -1 when the slice does not fit (the set then reads global memory).
+  auto stage = [&](const SetMeta &m, int *dst) -> int {
+    int send = m.end;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) send = max(send, __shfl_xor_sync(kFull, send, off));
+    const int sbeg = __shfl_sync(kFull, m.beg, 0);
+    if (send <= sbeg) return -1;
+    const int abase = col_aligned ? (sbeg & ~3) : sbeg;
+    const int count = send - abase;
+    if (count > slab) return -1;
+    if (col_aligned) {
+      for (int j = lane * 4; j < count; j += kWarp * 4) {
+        if (abase + j + 4 <= total_edges) {
+          cp_async_16(dst + j, a.col + abase + j);
+        } else {
+          for (int k = 0; k < 4; ++k)
+            if (abase + j + k < send) cp_async_4(dst + j + k, a.col + abase + j + k);
+        }
+      }
+    } else {
+      for (int j = lane; j < count; j += kWarp) cp_async_4(dst + j, a.col + abase + j);
+    }
+    return abase;
+  };
+
+  SetMeta m0 = load_set_meta<BWD>(a, set, nsets, G, sub, total_edges);
+  SetMeta m1 = load_set_meta<BWD>(a, set + stride, nsets, G, sub, total_edges);
+  int base0 = stage(m0, slab0);
+  cp_async_commit();
+  float wr0 = m0.row >= 0 ? __ldg(a.deg_row + m0.row) : 0.f;
+  int cur = 0;
+
+  for (; set < nsets; set += stride) {
+    const SetMeta m2 = load_set_meta<BWD>(a, set + 2 * stride, nsets, G, sub, total_edges);
+    const int base1 = stage(m1, slab0 + (cur ^ 1) * slab);
+    cp_async_commit();
+    const float wr1 = m1.row >= 0 ? __ldg(a.deg_row + m1.row) : 0.f;
+    cp_async_wait<1>();
+    __syncwarp();
+
+    const int len = m0.end - m0.beg;
+    int maxlen = len;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) maxlen = max(maxlen, __shfl_xor_sync(kFull, maxlen, off));
+    const bool staged = base0 >= 0;
+    const int *cs = staged ? slab0 + cur * slab + (m0.beg - base0) : a.col + m0.beg;
+
+    for (int tile = 0; tile < a.dim; tile += VEC * LPR) {
+      const int fcol = tile + sl * VEC;
+      const bool fact = fcol < a.dim && m0.row >= 0;
+      const float *fbase = a.feat + fcol;
+      float acc[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
+      for (int i0 = 0; i0 < maxlen; i0 += U) {
+        int c[U];
+        float w[U];
+        float v[U][VEC];
+#pragma unroll
+        for (int u = 0; u < U; ++u) c[u] = (fact && i0 + u < len) ? cs[i0 + u] : -1;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (c[u] >= 0) {
+            w[u] = __ldg(a.deg_col + c[u]);
+            load_vec<VEC>(fbase + static_cast<long long>(c[u]) * a.ld, v[u]);
+          } else {
+            w[u] = 0.f;
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float wj = __fmul_rn(wr0, w[u]);
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj, v[u][i], acc[i]);
+        }
+      }
+
+      // Segmented reduction over the sub-warps that share a row.
+      int rend = m0.end, rhi = m0.hi;
+#pragma unroll
+      for (int off = LPR; off < kWarp; off <<= 1) {
+        const int orow = __shfl_down_sync(kFull, m0.row, off);
+        const int oend = __shfl_down_sync(kFull, rend, off);
+        const int ohi = __shfl_down_sync(kFull, rhi, off);
+        float o[VEC];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[i] = __shfl_down_sync(kFull, acc[i], off);
+        if (lane + off < kWarp && m0.row >= 0 && orow == m0.row) {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) acc[i] += o[i];
+          rend = max(rend, oend);
+          rhi = ohi;
+        }
+      }
+      const int prow = __shfl_up_sync(kFull, m0.row, LPR);
+      const bool head = m0.row >= 0 && (sub == 0 || prow != m0.row);
+      if (head && fcol < a.dim) {
+        const bool whole = BWD ? (m0.lo != m0.row && rhi != m0.row) : (m0.beg == m0.lo && rend == m0.hi);
+        float *dst = a.out + static_cast<long long>(m0.row) * a.dim + fcol;
+        const int n = min(VEC, a.dim - fcol);
+        if (whole) store_row<VEC>(dst, acc, n, a.ovec);
+        else add_row<VEC>(dst, acc, n, a.ovec);
+      }
+    }
+    __syncwarp();   // everyone is done with the current slab before the next iteration refills it
+    m0 = m1; m1 = m2; base0 = base1; wr0 = wr1; cur ^= 1;
+  }
+  cp_async_wait<0>();
+}
+
+// 0: pick automatically, 1: one launch of non-persistent warps reading global
+// memory directly, 2: staged persistent kernel.  Read once from
+// EPPGCN_SPMM_KERNEL ("direct" / "staged"); meant for A/B measurements.
+int spmm_kernel_choice() {
+  static const int choice = [] {
+    const char *e = getenv("EPPGCN_SPMM_KERNEL");
+    if (!e) return 0;
+    if (!strcmp(e, "direct")) return 1;
+    if (!strcmp(e, "staged")) return 2;
+    return 0;
+  }();
+  return choice;
+}
+
+template <int VEC, int LPR, bool BWD>
+int launch_staged(const GroupArgs &a, int part_size, cudaStream_t s) {
+  constexpr int G = kWarp / LPR;
+  const int ps = part_size >= 1 ? part_size : 32;
+  long long want = static_cast<long long>(G) * ps + 4;
+  int slab = static_cast<int>(want > 1024 ? 1024 : (want + 3) / 4 * 4);
+  const int smem = slab * 2 * 8 * static_cast<int>(sizeof(int));
+  static int blocks_per_sm = 0;      // per instantiation; depends only on smem through `slab`, re-queried below
+  static int cached_smem = -1;
+  static int num_sms = 0;
+  if (cached_smem != smem) {
+    int dev = 0;
+    EPP_CUDA_TRY(cudaGetDevice(&dev));
+    EPP_CUDA_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+    if (smem > 48 * 1024)
+      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, BWD>,
+                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, staged_spmm_kernel<VEC, LPR, BWD>,
+                                                               256, smem));
+    if (blocks_per_sm < 1) blocks_per_sm = 1;
+    cached_smem = smem;
+  }
+  const long long nsets = ceil_div_ll(a.num_parts, G);
+  long long blocks = ceil_div_ll(nsets, 8);
+  const long long cap = static_cast<long long>(num_sms) * blocks_per_sm;
+  if (blocks > cap) blocks = cap;
+  const int col_aligned = aligned(a.col, 16) ? 1 : 0;
+  staged_spmm_kernel<VEC, LPR, BWD><<<static_cast<unsigned>(blocks), 256, smem, s>>>(a, slab, col_aligned);
+  EPP_CHECK_LAUNCH("staged_spmm_kernel");
+  return EPP_OK;
+}
+
+template <int VEC, bool BWD>
+int launch_staged_lpr(const GroupArgs &a, int lpr, int part_size, cudaStream_t s) {
+  switch (lpr) {
+    case 1:  return launch_staged<VEC, 1, BWD>(a, part_size, s);
+    case 2:  return launch_staged<VEC, 2, BWD>(a, part_size, s);
+    case 4:  return launch_staged<VEC, 4, BWD>(a, part_size, s);
+    case 8:  return launch_staged<VEC, 8, BWD>(a, part_size, s);
+    case 16: return launch_staged<VEC, 16, BWD>(a, part_size, s);
+    default: return launch_staged<VEC, 32, BWD>(a, part_size, s);
+  }
+}
+
 template <int VEC, bool BWD>
 int launch_lpr(const GroupArgs &a, int lpr, cudaStream_t s) {
   const long long groups_per_warp = kWarp / lpr;
@@ -209,10 +456,8 @@ int launch_lpr(const GroupArgs &a, int lpr, cudaStream_t s) {
   return EPP_OK;
 }
 
-inline bool aligned(const void *p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
-
 template <bool BWD>
-int launch_group_spmm(GroupArgs a, int num_rows, cudaStream_t s) {
+int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) {
   // Dense result: rows that no group touches, and rows that are accumulated
   // with atomics, start from zero.
   EPP_CUDA_TRY(cudaMemsetAsync(a.out, 0, sizeof(float) * static_cast<size_t>(num_rows) * a.dim, s));
@@ -227,6 +472,13 @@ int launch_group_spmm(GroupArgs a, int num_rows, cudaStream_t s) {
   const int lanes_needed = (a.dim + vec - 1) / vec;
   int lpr = 1;
   while (lpr < 32 && lpr < lanes_needed) lpr <<= 1;
+  if (spmm_kernel_choice() != 1) {
+    switch (vec) {
+      case 4:  return launch_staged_lpr<4, BWD>(a, lpr, part_size, s);
+      case 2:  return launch_staged_lpr<2, BWD>(a, lpr, part_size, s);
+      default: return launch_staged_lpr<1, BWD>(a, lpr, part_size, s);
+    }
+  }
   switch (vec) {
     case 4:  return launch_lpr<4, BWD>(a, lpr, s);
     case 2:  return launch_lpr<2, BWD>(a, lpr, s);
@@ -244,7 +496,7 @@ EPP_EXPORT int eppgcn_spmm_forward(float *out, const float *feat, long long feat
                                    int num_nodes, int dim, int num_parts,
                                    int part_size, int dim_worker, int warp_per_block,
                                    void *stream) {
-  (void)part_size; (void)dim_worker; (void)warp_per_block;
+  (void)dim_worker; (void)warp_per_block;
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(feat_ld >= dim, "feat_ld must be >= dim");
   if (num_nodes == 0) return EPP_OK;
@@ -254,7 +506,7 @@ EPP_EXPORT int eppgcn_spmm_forward(float *out, const float *feat, long long feat
   a.out = out; a.feat = feat; a.ld = feat_ld;
   a.part_ptr = part_ptr; a.row_of = part2node; a.row_ptr = row_ptr; a.col = col_idx;
   a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim;
-  return epp::launch_group_spmm<false>(a, num_nodes, static_cast<cudaStream_t>(stream));
+  return epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
 }
 
 EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
@@ -263,7 +515,7 @@ EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, l
                                               int num_nodes, int dim, int num_parts,
                                               int part_size, int blockx, int blocky,
                                               void *stream) {
-  (void)part_size; (void)blockx; (void)blocky;
+  (void)blockx; (void)blocky;
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(d_out_ld >= dim, "d_out_ld must be >= dim");
   if (num_nodes == 0) return EPP_OK;
@@ -273,5 +525,5 @@ EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, l
   a.out = d_in; a.feat = d_out; a.ld = d_out_ld;
   a.part_ptr = part_ptr; a.row_of = ids; a.row_ptr = nullptr; a.col = edge_list;
   a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim;
-  return epp::launch_group_spmm<true>(a, num_nodes, static_cast<cudaStream_t>(stream));
+  return epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
 }

@@ -65,22 +65,31 @@ def test_module_reproduces_reference_golden_vectors(gnna, cuda):
         assert np.array_equal(bb[2].cpu().numpy()[:e], z[f"bbp_part_pointer_{i}"])
         np.testing.assert_array_equal(bb[3].numpy(), z[f"bbp_info_{i}"].astype(np.float64))
         paths.append((ids, ppb, edges, int(pinfo[0].item())))
-    for conv, (rtol, atol) in (("rsqrt", (2e-5, 2e-6)), ("sqrt", (4e-5, 2e-3))):
+    # Both sides are fp32 with different summation orders.  With the reference loader's sqrt(deg)
+    # factors the terms of a sum reach 1e3..1e5 and cancel, so that convention is compared relative
+    # to the largest magnitude of each result; the normalising convention keeps the strict bound.
+    def check(got, want, strict, what):
+        got, want = got.cpu().numpy(), np.asarray(want)
+        s = 1.0 if strict else float(np.abs(want).max())
+        assert_close(got / s, want / s, 2e-5, 2e-6 if strict else 1e-5, what)
+
+    for conv in ("rsqrt", "sqrt"):
+        strict = conv == "rsqrt"
         deg = t(g[f"deg_{conv}"], cuda)
         h = t(g["x"], cuda)
         for i in range(L):
             w = t(g["ws"][i], cuda)
             y = gnna.forward(h, w, row, col, deg, pp, p2n, G.GPU_PART, 16, 4)[0]
-            assert_close(y.cpu().numpy(), z[f"forward_{conv}_{i}"], rtol, atol, f"forward {conv} {i}")
+            check(y, z[f"forward_{conv}_{i}"], strict, f"forward {conv} {i}")
             ids, ppb, edges, nparts = paths[i]
             d_in, d_w = gnna.ours_backward(t(g["d_outs"][i], cuda), h, w, ids, ppb, edges, deg, G.GPU_BACK,
                                            nparts, i + 1, 4, 16)
-            assert_close(d_in.cpu().numpy(), z[f"ours_backward_{conv}_{i}_dinput"], rtol, atol, "d_input")
+            check(d_in, z[f"ours_backward_{conv}_{i}_dinput"], strict, "d_input")
             scale = float(np.abs(z[f"ours_backward_{conv}_{i}_dweight"]).max())
             assert_close(d_w.cpu().numpy() / scale, z[f"ours_backward_{conv}_{i}_dweight"] / scale, 1e-4, 1e-5,
                          "d_weight")
             d_in, _ = gnna.backward(t(g["d_outs"][i], cuda), h, w, row, col, deg, pp, p2n, G.GPU_PART, 16, 4)
-            assert_close(d_in.cpu().numpy(), z[f"backward_{conv}_{i}_dinput"], rtol, atol, "backward")
+            check(d_in, z[f"backward_{conv}_{i}_dinput"], strict, "backward")
             h = torch.relu(t(z[f"forward_{conv}_{i}"], cuda))
 
 

@@ -269,6 +269,9 @@ def run_gpu(args):
             pass
 
     # -- e2e: host buffers through the C-ABI ------------------------------------
+    if args.kernels_only:
+        print(json.dumps({"value": round(ms_step, 4), "kernels": kernels, "roofline": roofline}), flush=True)
+        return
     host_in = [torch.empty(x.shape, pin_memory=True).copy_(x) for x in ins]
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
     stage = [padded(n, dims[0], dev, gen), padded(n, dims[1], dev, gen),
@@ -373,7 +376,11 @@ def main():
     p.add_argument("--backsize", type=int, default=32)
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-full-epoch", action="store_true")
+    p.add_argument("--kernels-only", action="store_true",
+                   help="device-resident timing only (no e2e, full-epoch or CPU legs); for profiler captures")
     args = p.parse_args()
+    if args.kernels_only:
+        args.no_cpu_baseline = args.no_full_epoch = True
     if args.impl == "reference":
         run_reference(args)
     else:

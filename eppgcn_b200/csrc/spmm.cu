@@ -246,10 +246,36 @@ __device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, long long s
   return m;
 }
 
+// N neighbour rows of one group, all loads issued before the first use.
+// `cs` points at the group's column ids (shared-memory slab or global memory).
+template <int VEC, int N>
+__device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, bool fact, const char *fbytes,
+                                             unsigned ld_bytes, const float *deg_col, float (&acc)[VEC]) {
+  int c[N];
+  float w[N];
+  float v[N][VEC];
+#pragma unroll
+  for (int u = 0; u < N; ++u) c[u] = (fact && i0 + u < len) ? cs[i0 + u] : -1;
+#pragma unroll
+  for (int u = 0; u < N; ++u) {
+    if (c[u] >= 0) {
+      w[u] = __ldg(deg_col + c[u]);
+      load_vec<VEC>(reinterpret_cast<const float *>(fbytes + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes), v[u]);
+    } else {
+      w[u] = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < N; ++u)
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
+}
+
 template <int VEC, int LPR, bool BWD>
 __global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, const int slab, const int col_aligned) {
   constexpr int G = kWarp / LPR;
-  constexpr int U = 8;
   extern __shared__ __align__(16) int s_cols[];
   const int lane = threadIdx.x & 31;
   const int sub = lane / LPR;
@@ -262,13 +288,12 @@ __global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, con
   long long set = static_cast<long long>(blockIdx.x) * wpb + wib;
   if (set >= nsets) return;
   const int total_edges = __ldg(a.part_ptr + a.num_parts);
+  const unsigned ld_bytes = static_cast<unsigned>(a.ld) * 4u;
 
   // Starts the copy of one set's column ids; returns the first edge held by the
   // slab, or -1 when the slice does not fit (the set then reads global memory).
   auto stage = [&](const SetMeta &m, int *dst) -> int {
-    int send = m.end;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) send = max(send, __shfl_xor_sync(kFull, send, off));
+    const int send = __reduce_max_sync(kFull, m.end);
     const int sbeg = __shfl_sync(kFull, m.beg, 0);
     if (send <= sbeg) return -1;
     const int abase = col_aligned ? (sbeg & ~3) : sbeg;
@@ -305,64 +330,51 @@ __global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, con
     __syncwarp();
 
     const int len = m0.end - m0.beg;
-    int maxlen = len;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) maxlen = max(maxlen, __shfl_xor_sync(kFull, maxlen, off));
-    const bool staged = base0 >= 0;
-    const int *cs = staged ? slab0 + cur * slab + (m0.beg - base0) : a.col + m0.beg;
+    const int maxlen = __reduce_max_sync(kFull, len);
+    const int *cs = base0 >= 0 ? slab0 + cur * slab + (m0.beg - base0) : a.col + m0.beg;
+    // Sub-warps with the same row are neighbours; when no two neighbours agree the
+    // shuffle reduction below has nothing to combine and is skipped.
+    const int prow = __shfl_up_sync(kFull, m0.row, LPR);
+    const bool cont = sub > 0 && m0.row >= 0 && prow == m0.row;
+    const bool any_run = __any_sync(kFull, cont);
 
+#pragma unroll 1
     for (int tile = 0; tile < a.dim; tile += VEC * LPR) {
       const int fcol = tile + sl * VEC;
       const bool fact = fcol < a.dim && m0.row >= 0;
-      const float *fbase = a.feat + fcol;
+      const char *fbytes = reinterpret_cast<const char *>(a.feat + fcol);
       float acc[VEC];
 #pragma unroll
       for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-      for (int i0 = 0; i0 < maxlen; i0 += U) {
-        int c[U];
-        float w[U];
-        float v[U][VEC];
+      int i0 = 0;
+#pragma unroll 1
+      for (; i0 + 8 <= maxlen; i0 += 8) gather_batch<VEC, 8>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc);
+      // warp-uniform tail: 4 + 2 + 1 covers any remainder below 8
+      if (maxlen - i0 >= 4) { gather_batch<VEC, 4>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); i0 += 4; }
+      if (maxlen - i0 >= 2) { gather_batch<VEC, 2>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); i0 += 2; }
+      if (maxlen - i0 >= 1) { gather_batch<VEC, 1>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); }
 #pragma unroll
-        for (int u = 0; u < U; ++u) c[u] = (fact && i0 + u < len) ? cs[i0 + u] : -1;
+      for (int i = 0; i < VEC; ++i) acc[i] *= wr0;
+
+      int rend = m0.end, rhi = m0.hi;
+      if (any_run) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (c[u] >= 0) {
-            w[u] = __ldg(a.deg_col + c[u]);
-            load_vec<VEC>(fbase + static_cast<long long>(c[u]) * a.ld, v[u]);
-          } else {
-            w[u] = 0.f;
+        for (int off = LPR; off < kWarp; off <<= 1) {
+          const int orow = __shfl_down_sync(kFull, m0.row, off);
+          const int oend = __shfl_down_sync(kFull, rend, off);
+          const int ohi = __shfl_down_sync(kFull, rhi, off);
+          float o[VEC];
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+          for (int i = 0; i < VEC; ++i) o[i] = __shfl_down_sync(kFull, acc[i], off);
+          if (lane + off < kWarp && m0.row >= 0 && orow == m0.row) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) acc[i] += o[i];
+            rend = max(rend, oend);
+            rhi = ohi;
           }
         }
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float wj = __fmul_rn(wr0, w[u]);
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj, v[u][i], acc[i]);
-        }
       }
-
-      // Segmented reduction over the sub-warps that share a row.
-      int rend = m0.end, rhi = m0.hi;
-#pragma unroll
-      for (int off = LPR; off < kWarp; off <<= 1) {
-        const int orow = __shfl_down_sync(kFull, m0.row, off);
-        const int oend = __shfl_down_sync(kFull, rend, off);
-        const int ohi = __shfl_down_sync(kFull, rhi, off);
-        float o[VEC];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = __shfl_down_sync(kFull, acc[i], off);
-        if (lane + off < kWarp && m0.row >= 0 && orow == m0.row) {
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] += o[i];
-          rend = max(rend, oend);
-          rhi = ohi;
-        }
-      }
-      const int prow = __shfl_up_sync(kFull, m0.row, LPR);
-      const bool head = m0.row >= 0 && (sub == 0 || prow != m0.row);
-      if (head && fcol < a.dim) {
+      if (m0.row >= 0 && !cont && fcol < a.dim) {
         const bool whole = BWD ? (m0.lo != m0.row && rhi != m0.row) : (m0.beg == m0.lo && rend == m0.hi);
         float *dst = a.out + static_cast<long long>(m0.row) * a.dim + fcol;
         const int n = min(VEC, a.dim - fcol);

@@ -12,7 +12,8 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libeppgcn_b200.so")
+# EPPGCN_B200_LIB points at another build of the same library (an experimental kernel variant).
+LIB_PATH = os.environ.get("EPPGCN_B200_LIB") or os.path.join(_HERE, "libeppgcn_b200.so")
 
 EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE = range(5)
 

@@ -1,30 +1,35 @@
 // Neighbour-group aggregation kernels for sm_100a: the forward SpMM over the
 // build_part groups and the backward SpMM over the compacted execution path.
 //
-// Both directions run one kernel template.  A "sub-warp" of LPR lanes owns one
-// group (at most part_size consecutive edges of one row); each lane owns VEC
-// consecutive feature columns, so a neighbour row is fetched with one 4/8/16
-// byte load per lane and one warp-level load instruction gathers 32/LPR
-// different neighbour rows.  Column ids and the edge weight deg[r]*deg[c] are
-// loaded once per edge by one lane and broadcast with shuffles.  After the
-// edge loop the sub-warps of a warp that worked on the same row are combined
-// with a segmented shuffle reduction, and only the head of each run touches
-// memory: a plain vector store when the run covers the whole row, a vector
-// atomic add otherwise (a row split across warps).
-#include <stdlib.h>
-#include <string.h>
-
+// Both directions run one persistent kernel template.
+//
+// Mapping.  A "sub-warp" of LPR lanes owns one group (at most part_size
+// consecutive edges of one row) at a time; a lane owns T tiles of VEC
+// consecutive feature columns (tile k starts at column (k*LPR + lane)*VEC), so
+// one warp-level load instruction fetches VEC*LPR*4 contiguous bytes of
+// 32/LPR different neighbour rows.  Narrow rows (16 or 22 floats) use 4 lanes
+// per row, i.e. 8 rows per warp instruction; wide rows keep 4 lanes and add
+// tiles, so the per-edge index work is amortised over more bytes.
+//
+// Staging.  A warp walks over "sets" of 32/LPR consecutive groups.  The column
+// ids of a set are one contiguous slice of the edge array; the warp copies that
+// slice into its private shared-memory slab with cp.async while it is still
+// busy with the previous set (two slabs per warp), and the group descriptors of
+// the set after that are already on their way in registers.  Inside a set the
+// only exposed memory latency is the gather itself: a lane keeps up to eight
+// 16-byte row loads in flight, reads the column id as a shared-memory
+// broadcast and the source-side degree as a sub-warp-uniform cached load.
+//
+// Reduction.  After the edge loop the sub-warps of a warp that worked on the
+// same row are combined with a segmented shuffle reduction, and only the head
+// of each run touches memory: a plain vector store when the run covers the
+// whole row, a vector atomic add otherwise (a row split across warps).
 #include "common.cuh"
 
 namespace epp {
 namespace {
 
 inline bool aligned(const void *p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
-
-template <int VEC> struct VecT;
-template <> struct VecT<4> { using type = float4; };
-template <> struct VecT<2> { using type = float2; };
-template <> struct VecT<1> { using type = float; };
 
 template <int VEC>
 __device__ __forceinline__ void load_vec(const float *p, float (&v)[VEC]) {
@@ -76,7 +81,7 @@ struct GroupArgs {
   long long ld;
   const int *part_ptr;     // [num_parts+1]
   const int *row_of;       // forward: part2node[num_parts]; backward: ids[] per compacted edge
-  const int *row_ptr;      // forward only
+  const int *row_ptr;      // forward only (kept for callers; the kernel derives row extents from the groups)
   const int *col;          // column id per edge
   const float *deg_row;
   const float *deg_col;
@@ -85,125 +90,6 @@ struct GroupArgs {
   int ovec;                // widest aligned access into `out`: 4, 2 or 1 floats
 };
 
-// BWD = false: groups (part_ptr, part2node) over a CSR (row_ptr).
-// BWD = true : parts over the compacted edge list; the row of a part is
-//              ids[part_ptr[p]] and the extent of a row is found by looking at
-//              the ids on either side of the run.
-template <int VEC, int LPR, bool BWD>
-__global__ void __launch_bounds__(256) group_spmm_kernel(const GroupArgs a) {
-  constexpr int G = kWarp / LPR;          // groups per warp
-  constexpr int U = LPR < 8 ? LPR : 8;    // neighbour rows in flight per lane
-  const int lane = threadIdx.x & 31;
-  const int sub = lane / LPR;
-  const int sl = lane % LPR;
-  const long long warp = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const long long g = warp * G + sub;
-
-  int beg = 0, end = 0, row = -1;
-  if (g < a.num_parts) {
-    beg = __ldg(a.part_ptr + g);
-    end = __ldg(a.part_ptr + g + 1);
-    if (end > beg) row = BWD ? __ldg(a.row_of + beg) : __ldg(a.row_of + g);
-    else end = beg;
-  }
-  const float wr = row >= 0 ? __ldg(a.deg_row + row) : 0.f;
-  int iters = (end - beg + LPR - 1) / LPR;
-#pragma unroll
-  for (int off = 16; off >= 1; off >>= 1) iters = max(iters, __shfl_xor_sync(kFull, iters, off));
-
-  // Run bookkeeping is the same for every column tile; computed once below.
-  int run_end = end;
-  bool head = false, whole = false;
-
-  for (int tile = 0; tile < a.dim; tile += VEC * LPR) {
-    const int fcol = tile + sl * VEC;
-    const bool fact = fcol < a.dim;
-    float acc[VEC];
-#pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-
-    for (int it = 0; it < iters; ++it) {
-      const int e0 = beg + it * LPR;
-      const int e = e0 + sl;
-      int c = 0;
-      float w = 0.f;
-      if (e < end) {
-        c = __ldg(a.col + e);
-        w = __fmul_rn(wr, __ldg(a.deg_col + c));
-      }
-#pragma unroll
-      for (int j0 = 0; j0 < LPR; j0 += U) {
-        float v[U][VEC];
-        float wj[U];
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int cj = __shfl_sync(kFull, c, j0 + u, LPR);
-          wj[u] = __shfl_sync(kFull, w, j0 + u, LPR);
-          if (fact && e0 + j0 + u < end) {
-            load_vec<VEC>(a.feat + static_cast<long long>(cj) * a.ld + fcol, v[u]);
-          } else {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
-            wj[u] = 0.f;
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < U; ++u)
-#pragma unroll
-          for (int i = 0; i < VEC; ++i) acc[i] = fmaf(wj[u], v[u][i], acc[i]);
-      }
-    }
-
-    // Segmented reduction over the sub-warps of this warp that share a row.
-    int rend = end;
-#pragma unroll
-    for (int off = LPR; off < kWarp; off <<= 1) {
-      const int orow = __shfl_down_sync(kFull, row, off);
-      const int oend = __shfl_down_sync(kFull, rend, off);
-      float o[VEC];
-#pragma unroll
-      for (int i = 0; i < VEC; ++i) o[i] = __shfl_down_sync(kFull, acc[i], off);
-      if (lane + off < kWarp && row >= 0 && orow == row) {
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) acc[i] += o[i];
-        rend = max(rend, oend);
-      }
-    }
-    if (tile == 0) {
-      run_end = rend;
-      const int prow = __shfl_up_sync(kFull, row, LPR);
-      head = row >= 0 && (sub == 0 || prow != row);
-      if (head) {
-        if (BWD) {
-          const int total = __ldg(a.part_ptr + a.num_parts);
-          whole = (beg == 0 || __ldg(a.row_of + beg - 1) != row) &&
-                  (run_end >= total || __ldg(a.row_of + run_end) != row);
-        } else {
-          whole = beg == __ldg(a.row_ptr + row) && run_end == __ldg(a.row_ptr + row + 1);
-        }
-      }
-    }
-    if (head && fact) {
-      float *dst = a.out + static_cast<long long>(row) * a.dim + fcol;
-      const int n = min(VEC, a.dim - fcol);
-      if (whole) store_row<VEC>(dst, acc, n, a.ovec);
-      else add_row<VEC>(dst, acc, n, a.ovec);
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-// Staged, persistent variant.
-//
-// A warp walks over "sets" of G = 32/LPR consecutive groups.  The column ids of
-// a set are one contiguous slice of the edge array; the warp copies that slice
-// into its private shared-memory slab with cp.async while it is still busy with
-// the previous set (two slabs per warp), and the group descriptors of the set
-// after that are already on their way in registers.  Inside a set the only
-// exposed memory latency is therefore the gather itself: every lane keeps
-// eight neighbour rows in flight, reads the column id as a shared-memory
-// broadcast and the source-side degree as a (sub-warp uniform) cached load.
-// ---------------------------------------------------------------------------
 __device__ __forceinline__ void cp_async_4(int *smem_dst, const int *gmem_src) {
   const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
@@ -218,64 +104,89 @@ __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_gr
 
 struct SetMeta {
   int beg, end, row;   // this sub-warp's group: edge range and destination row (-1: nothing to do)
-  int lo, hi;          // forward: row_ptr[row], row_ptr[row+1]; backward: row id of the edge before / after
+  int lo, hi;          // row of the group before / after this one (-1 at either end of the list)
 };
 
+// BWD = false: groups (part_ptr, part2node) from build_part.  A row's groups are
+//              consecutive, so a run of groups covers its whole row exactly when
+//              the groups on either side belong to other rows.
+// BWD = true : parts over the compacted edge list; the row of a part is
+//              ids[part_ptr[p]], and the rows on either side are the ids of the
+//              edge before the part and of the edge after it.
 template <bool BWD>
-__device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, long long set, long long nsets, int groups,
-                                                 int sub, int total_edges) {
+__device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, int g, int total_edges) {
   SetMeta m{0, 0, -1, -1, -1};
-  const long long g = set * groups + sub;
-  if (set < nsets && g < a.num_parts) {
+  if (g < a.num_parts) {
     m.beg = __ldg(a.part_ptr + g);
     m.end = __ldg(a.part_ptr + g + 1);
-    if (m.end > m.beg) {
-      if (BWD) {
+    if (BWD) {
+      if (m.end > m.beg) {
         m.row = __ldg(a.row_of + m.beg);
         m.lo = m.beg > 0 ? __ldg(a.row_of + m.beg - 1) : -1;
         m.hi = m.end < total_edges ? __ldg(a.row_of + m.end) : -1;
-      } else {
-        m.row = __ldg(a.row_of + g);
-        m.lo = __ldg(a.row_ptr + m.row);
-        m.hi = __ldg(a.row_ptr + m.row + 1);
       }
     } else {
-      m.end = m.beg;
+      m.row = __ldg(a.row_of + g);
+      m.lo = g > 0 ? __ldg(a.row_of + g - 1) : -1;
+      m.hi = g + 1 < a.num_parts ? __ldg(a.row_of + g + 1) : -1;
     }
+    if (m.end <= m.beg) { m.end = m.beg; m.row = -1; }
   }
   return m;
 }
 
-// N neighbour rows of one group, all loads issued before the first use.
-// `cs` points at the group's column ids (shared-memory slab or global memory).
-template <int VEC, int N>
-__device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, bool fact, const char *fbytes,
-                                             unsigned ld_bytes, const float *deg_col, float (&acc)[VEC]) {
+// N edges of one group: all loads are issued before the first use.  `cs` points
+// at the group's column ids (shared-memory slab, or global memory when the set
+// did not fit its slab).  FULL: every sub-warp of the warp has all N edges and
+// every lane all T tiles, so nothing is tested.  `tiles` is the lane's bit mask
+// of tiles that hold feature columns.
+template <int VEC, int T, int N, bool FULL>
+__device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, unsigned tiles, const char *fbytes,
+                                             unsigned ld_bytes, unsigned tile_bytes, const float *deg_col,
+                                             float (&acc)[T][VEC]) {
   int c[N];
   float w[N];
-  float v[N][VEC];
+  float v[N][T][VEC];
 #pragma unroll
-  for (int u = 0; u < N; ++u) c[u] = (fact && i0 + u < len) ? cs[i0 + u] : -1;
+  for (int u = 0; u < N; ++u) c[u] = (FULL || i0 + u < len) ? cs[i0 + u] : -1;
 #pragma unroll
   for (int u = 0; u < N; ++u) {
-    if (c[u] >= 0) {
+    if (FULL || c[u] >= 0) {
       w[u] = __ldg(deg_col + c[u]);
-      load_vec<VEC>(reinterpret_cast<const float *>(fbytes + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes), v[u]);
+      const char *rowp = fbytes + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes;
+#pragma unroll
+      for (int k = 0; k < T; ++k) {
+        if (FULL || (tiles >> k) & 1u) {
+          load_vec<VEC>(reinterpret_cast<const float *>(rowp + k * tile_bytes), v[u][k]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) v[u][k][i] = 0.f;
+        }
+      }
     } else {
       w[u] = 0.f;
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) v[u][i] = 0.f;
+      for (int k = 0; k < T; ++k)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[u][k][i] = 0.f;
     }
   }
 #pragma unroll
   for (int u = 0; u < N; ++u)
 #pragma unroll
-    for (int i = 0; i < VEC; ++i) acc[i] = fmaf(w[u], v[u][i], acc[i]);
+    for (int k = 0; k < T; ++k)
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) acc[k][i] = fmaf(w[u], v[u][k][i], acc[k][i]);
 }
 
-template <int VEC, int LPR, bool BWD>
-__global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, const int slab, const int col_aligned) {
-  constexpr int G = kWarp / LPR;
+// One launch covers feature columns [0, min(dim_left, VEC*LPR*T)) of the
+// pointers it is given; wider rows are handled by the host with further
+// launches on shifted pointers.
+template <int VEC, int LPR, int T, bool BWD>
+__global__ void __launch_bounds__(256, (T <= 4 ? 3 : 2))
+staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int col_aligned) {
+  constexpr int G = kWarp / LPR;               // groups per set
+  constexpr int U = T >= 8 ? 1 : 8 / T;        // edges per batch: U*T row loads in flight per lane
   extern __shared__ __align__(16) int s_cols[];
   const int lane = threadIdx.x & 31;
   const int sub = lane / LPR;
@@ -283,103 +194,123 @@ __global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, con
   const int wib = threadIdx.x >> 5;
   const int wpb = blockDim.x >> 5;
   int *const slab0 = s_cols + (wib * 2) * slab;   // this warp's two slabs: slab0 + cur * slab
-  const long long nsets = (static_cast<long long>(a.num_parts) + G - 1) / G;
-  const long long stride = static_cast<long long>(gridDim.x) * wpb;
-  long long set = static_cast<long long>(blockIdx.x) * wpb + wib;
+  const int nsets = (a.num_parts + G - 1) / G;
+  const int stride = gridDim.x * wpb;
+  int set = blockIdx.x * wpb + wib;
   if (set >= nsets) return;
   const int total_edges = __ldg(a.part_ptr + a.num_parts);
   const unsigned ld_bytes = static_cast<unsigned>(a.ld) * 4u;
+  constexpr unsigned tile_bytes = VEC * LPR * 4u;
+
+  // Column ownership of this lane: the same for every set.
+  const int fcol = sl * VEC;
+  unsigned tiles = 0;
+#pragma unroll
+  for (int k = 0; k < T; ++k)
+    if (fcol + k * VEC * LPR < cols) tiles |= 1u << k;
+  const bool all_tiles = __all_sync(kFull, tiles == (1u << T) - 1u);
+  const char *fbytes = reinterpret_cast<const char *>(a.feat + fcol);
 
   // Starts the copy of one set's column ids; returns the first edge held by the
-  // slab, or -1 when the slice does not fit (the set then reads global memory).
+  // slab, or -1 when the slice cannot be staged (too long for the slab, or its
+  // last 16-byte chunk would reach past the edge array); such a set reads its
+  // column ids from global memory.
   auto stage = [&](const SetMeta &m, int *dst) -> int {
     const int send = __reduce_max_sync(kFull, m.end);
     const int sbeg = __shfl_sync(kFull, m.beg, 0);
-    if (send <= sbeg) return -1;
-    const int abase = col_aligned ? (sbeg & ~3) : sbeg;
-    const int count = send - abase;
-    if (count > slab) return -1;
     if (col_aligned) {
-      for (int j = lane * 4; j < count; j += kWarp * 4) {
-        if (abase + j + 4 <= total_edges) {
-          cp_async_16(dst + j, a.col + abase + j);
-        } else {
-          for (int k = 0; k < 4; ++k)
-            if (abase + j + k < send) cp_async_4(dst + j + k, a.col + abase + j + k);
-        }
-      }
-    } else {
-      for (int j = lane; j < count; j += kWarp) cp_async_4(dst + j, a.col + abase + j);
+      const int abase = sbeg & ~3;
+      const int count = (send - abase + 3) & ~3;
+      if (send <= sbeg || count > slab || abase + count > total_edges) return -1;
+      for (int j = lane * 4; j < count; j += kWarp * 4) cp_async_16(dst + j, a.col + abase + j);
+      return abase;
     }
-    return abase;
+    const int count = send - sbeg;
+    if (count <= 0 || count > slab) return -1;
+    for (int j = lane; j < count; j += kWarp) cp_async_4(dst + j, a.col + sbeg + j);
+    return sbeg;
   };
 
-  SetMeta m0 = load_set_meta<BWD>(a, set, nsets, G, sub, total_edges);
-  SetMeta m1 = load_set_meta<BWD>(a, set + stride, nsets, G, sub, total_edges);
+  SetMeta m0 = load_set_meta<BWD>(a, set * G + sub, total_edges);
+  SetMeta m1 = load_set_meta<BWD>(a, set + stride < nsets ? (set + stride) * G + sub : a.num_parts, total_edges);
   int base0 = stage(m0, slab0);
   cp_async_commit();
   float wr0 = m0.row >= 0 ? __ldg(a.deg_row + m0.row) : 0.f;
   int cur = 0;
 
   for (; set < nsets; set += stride) {
-    const SetMeta m2 = load_set_meta<BWD>(a, set + 2 * stride, nsets, G, sub, total_edges);
+    const int set2 = set + 2 * stride;
+    const SetMeta m2 = load_set_meta<BWD>(a, set2 < nsets ? set2 * G + sub : a.num_parts, total_edges);
     const int base1 = stage(m1, slab0 + (cur ^ 1) * slab);
     cp_async_commit();
     const float wr1 = m1.row >= 0 ? __ldg(a.deg_row + m1.row) : 0.f;
     cp_async_wait<1>();
     __syncwarp();
 
-    const int len = m0.end - m0.beg;
+    const int len = (tiles && m0.row >= 0) ? m0.end - m0.beg : 0;   // lanes without columns gather nothing
     const int maxlen = __reduce_max_sync(kFull, len);
+    const int minlen = all_tiles ? __reduce_min_sync(kFull, len) : 0;
     const int *cs = base0 >= 0 ? slab0 + cur * slab + (m0.beg - base0) : a.col + m0.beg;
-    // Sub-warps with the same row are neighbours; when no two neighbours agree the
-    // shuffle reduction below has nothing to combine and is skipped.
-    const int prow = __shfl_up_sync(kFull, m0.row, LPR);
-    const bool cont = sub > 0 && m0.row >= 0 && prow == m0.row;
-    const bool any_run = __any_sync(kFull, cont);
 
-#pragma unroll 1
-    for (int tile = 0; tile < a.dim; tile += VEC * LPR) {
-      const int fcol = tile + sl * VEC;
-      const bool fact = fcol < a.dim && m0.row >= 0;
-      const char *fbytes = reinterpret_cast<const char *>(a.feat + fcol);
-      float acc[VEC];
+    float acc[T][VEC];
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] = 0.f;
-      int i0 = 0;
-#pragma unroll 1
-      for (; i0 + 8 <= maxlen; i0 += 8) gather_batch<VEC, 8>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc);
-      // warp-uniform tail: 4 + 2 + 1 covers any remainder below 8
-      if (maxlen - i0 >= 4) { gather_batch<VEC, 4>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); i0 += 4; }
-      if (maxlen - i0 >= 2) { gather_batch<VEC, 2>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); i0 += 2; }
-      if (maxlen - i0 >= 1) { gather_batch<VEC, 1>(cs, i0, len, fact, fbytes, ld_bytes, a.deg_col, acc); }
+    for (int k = 0; k < T; ++k)
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[i] *= wr0;
+      for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
 
-      int rend = m0.end, rhi = m0.hi;
-      if (any_run) {
+    int i0 = 0;
+#pragma unroll 1
+    for (; i0 + U <= minlen; i0 += U)
+      gather_batch<VEC, T, U, true>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+#pragma unroll 1
+    for (; i0 + U <= maxlen; i0 += U)
+      gather_batch<VEC, T, U, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+    // warp-uniform tail: 4 + 2 + 1 covers any remainder below 8
+    if (U > 4 && maxlen - i0 >= 4) {
+      gather_batch<VEC, T, 4, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      i0 += 4;
+    }
+    if (U > 2 && maxlen - i0 >= 2) {
+      gather_batch<VEC, T, 2, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      i0 += 2;
+    }
+    if (U > 1 && maxlen - i0 >= 1)
+      gather_batch<VEC, T, 1, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
 #pragma unroll
-        for (int off = LPR; off < kWarp; off <<= 1) {
-          const int orow = __shfl_down_sync(kFull, m0.row, off);
-          const int oend = __shfl_down_sync(kFull, rend, off);
-          const int ohi = __shfl_down_sync(kFull, rhi, off);
-          float o[VEC];
+    for (int k = 0; k < T; ++k)
 #pragma unroll
-          for (int i = 0; i < VEC; ++i) o[i] = __shfl_down_sync(kFull, acc[i], off);
-          if (lane + off < kWarp && m0.row >= 0 && orow == m0.row) {
+      for (int i = 0; i < VEC; ++i) acc[k][i] *= wr0;
+
+    // Sub-warps with the same row are neighbours (lo of one is the row of the
+    // one before); when no two neighbours agree there is nothing to combine.
+    const bool cont = sub > 0 && m0.row >= 0 && m0.lo == m0.row;
+    int rhi = m0.hi;
+    if (__any_sync(kFull, cont)) {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) acc[i] += o[i];
-            rend = max(rend, oend);
-            rhi = ohi;
+      for (int off = LPR; off < kWarp; off <<= 1) {
+        const int orow = __shfl_down_sync(kFull, m0.row, off);
+        const int ohi = __shfl_down_sync(kFull, rhi, off);
+        const bool take = lane + off < kWarp && m0.row >= 0 && orow == m0.row;
+#pragma unroll
+        for (int k = 0; k < T; ++k)
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) {
+            const float o = __shfl_down_sync(kFull, acc[k][i], off);
+            if (take) acc[k][i] += o;
           }
-        }
+        if (take) rhi = ohi;
       }
-      if (m0.row >= 0 && !cont && fcol < a.dim) {
-        const bool whole = BWD ? (m0.lo != m0.row && rhi != m0.row) : (m0.beg == m0.lo && rend == m0.hi);
-        float *dst = a.out + static_cast<long long>(m0.row) * a.dim + fcol;
-        const int n = min(VEC, a.dim - fcol);
-        if (whole) store_row<VEC>(dst, acc, n, a.ovec);
-        else add_row<VEC>(dst, acc, n, a.ovec);
+    }
+    if (m0.row >= 0 && !cont && tiles) {
+      const bool whole = m0.lo != m0.row && rhi != m0.row;
+      float *dst = a.out + static_cast<long long>(m0.row) * a.dim + fcol;
+#pragma unroll
+      for (int k = 0; k < T; ++k) {
+        if ((tiles >> k) & 1u) {
+          const int n = min(VEC, cols - (fcol + k * VEC * LPR));
+          if (whole) store_row<VEC>(dst + k * VEC * LPR, acc[k], n, a.ovec);
+          else add_row<VEC>(dst + k * VEC * LPR, acc[k], n, a.ovec);
+        }
       }
     }
     __syncwarp();   // everyone is done with the current slab before the next iteration refills it
@@ -388,84 +319,62 @@ __global__ void __launch_bounds__(256) staged_spmm_kernel(const GroupArgs a, con
   cp_async_wait<0>();
 }
 
-// 0: pick automatically, 1: one launch of non-persistent warps reading global
-// memory directly, 2: staged persistent kernel.  Read once from
-// EPPGCN_SPMM_KERNEL ("direct" / "staged"); meant for A/B measurements.
-int spmm_kernel_choice() {
-  static const int choice = [] {
-    const char *e = getenv("EPPGCN_SPMM_KERNEL");
-    if (!e) return 0;
-    if (!strcmp(e, "direct")) return 1;
-    if (!strcmp(e, "staged")) return 2;
-    return 0;
-  }();
-  return choice;
-}
+struct LaunchInfo {
+  int blocks_per_sm = 0;
+  int smem = -1;
+  int num_sms = 0;
+};
 
-template <int VEC, int LPR, bool BWD>
-int launch_staged(const GroupArgs &a, int part_size, cudaStream_t s) {
+template <int VEC, int LPR, int T, bool BWD>
+int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
   constexpr int G = kWarp / LPR;
+  constexpr int SPAN = VEC * LPR * T;           // feature columns per launch
   const int ps = part_size >= 1 ? part_size : 32;
-  long long want = static_cast<long long>(G) * ps + 4;
-  int slab = static_cast<int>(want > 1024 ? 1024 : (want + 3) / 4 * 4);
+  const long long want = static_cast<long long>(G) * ps + 8;
+  const int slab = static_cast<int>(want > 1024 ? 1024 : (want + 3) / 4 * 4);
   const int smem = slab * 2 * 8 * static_cast<int>(sizeof(int));
-  static int blocks_per_sm = 0;      // per instantiation; depends only on smem through `slab`, re-queried below
-  static int cached_smem = -1;
-  static int num_sms = 0;
-  if (cached_smem != smem) {
+  static LaunchInfo info;              // per instantiation; the occupancy query is repeated when smem changes
+  if (info.smem != smem) {
     int dev = 0;
     EPP_CUDA_TRY(cudaGetDevice(&dev));
-    EPP_CUDA_TRY(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+    EPP_CUDA_TRY(cudaDeviceGetAttribute(&info.num_sms, cudaDevAttrMultiProcessorCount, dev));
     if (smem > 48 * 1024)
-      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, BWD>,
+      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, T, BWD>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks_per_sm, staged_spmm_kernel<VEC, LPR, BWD>,
-                                                               256, smem));
-    if (blocks_per_sm < 1) blocks_per_sm = 1;
-    cached_smem = smem;
+    EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&info.blocks_per_sm,
+                                                               staged_spmm_kernel<VEC, LPR, T, BWD>, 256, smem));
+    if (info.blocks_per_sm < 1) info.blocks_per_sm = 1;
+    info.smem = smem;
   }
-  const long long nsets = ceil_div_ll(a.num_parts, G);
+  const long long nsets = ceil_div_ll(a0.num_parts, G);
   long long blocks = ceil_div_ll(nsets, 8);
-  const long long cap = static_cast<long long>(num_sms) * blocks_per_sm;
+  const long long cap = static_cast<long long>(info.num_sms) * info.blocks_per_sm;
   if (blocks > cap) blocks = cap;
-  const int col_aligned = aligned(a.col, 16) ? 1 : 0;
-  staged_spmm_kernel<VEC, LPR, BWD><<<static_cast<unsigned>(blocks), 256, smem, s>>>(a, slab, col_aligned);
-  EPP_CHECK_LAUNCH("staged_spmm_kernel");
+  const int col_aligned = aligned(a0.col, 16) ? 1 : 0;
+  for (int col0 = 0; col0 < a0.dim; col0 += SPAN) {     // one launch unless the row is wider than SPAN
+    GroupArgs a = a0;
+    a.feat = a0.feat + col0;
+    a.out = a0.out + col0;
+    const int cols = a0.dim - col0 < SPAN ? a0.dim - col0 : SPAN;
+    staged_spmm_kernel<VEC, LPR, T, BWD><<<static_cast<unsigned>(blocks), 256, smem, s>>>(a, cols, slab, col_aligned);
+    EPP_CHECK_LAUNCH("staged_spmm_kernel");
+  }
   return EPP_OK;
 }
 
+// Lanes per row and tiles per lane for a row of `lanes_needed` VEC-wide pieces.
 template <int VEC, bool BWD>
-int launch_staged_lpr(const GroupArgs &a, int lpr, int part_size, cudaStream_t s) {
-  switch (lpr) {
-    case 1:  return launch_staged<VEC, 1, BWD>(a, part_size, s);
-    case 2:  return launch_staged<VEC, 2, BWD>(a, part_size, s);
-    case 4:  return launch_staged<VEC, 4, BWD>(a, part_size, s);
-    case 8:  return launch_staged<VEC, 8, BWD>(a, part_size, s);
-    case 16: return launch_staged<VEC, 16, BWD>(a, part_size, s);
-    default: return launch_staged<VEC, 32, BWD>(a, part_size, s);
-  }
-}
-
-template <int VEC, bool BWD>
-int launch_lpr(const GroupArgs &a, int lpr, cudaStream_t s) {
-  const long long groups_per_warp = kWarp / lpr;
-  const long long warps = ceil_div_ll(a.num_parts, groups_per_warp);
-  const long long blocks = ceil_div_ll(warps, 8);
-  if (blocks > 0x7fffffffLL) {
-    set_error("too many groups for one launch");
-    return EPP_ERR_TOO_LARGE;
-  }
-  const dim3 grid(static_cast<unsigned>(blocks)), block(256);
-  switch (lpr) {
-    case 1:  group_spmm_kernel<VEC, 1, BWD><<<grid, block, 0, s>>>(a); break;
-    case 2:  group_spmm_kernel<VEC, 2, BWD><<<grid, block, 0, s>>>(a); break;
-    case 4:  group_spmm_kernel<VEC, 4, BWD><<<grid, block, 0, s>>>(a); break;
-    case 8:  group_spmm_kernel<VEC, 8, BWD><<<grid, block, 0, s>>>(a); break;
-    case 16: group_spmm_kernel<VEC, 16, BWD><<<grid, block, 0, s>>>(a); break;
-    default: group_spmm_kernel<VEC, 32, BWD><<<grid, block, 0, s>>>(a); break;
-  }
-  EPP_CHECK_LAUNCH("group_spmm_kernel");
-  return EPP_OK;
+int launch_shape(const GroupArgs &a, int lanes_needed, int part_size, cudaStream_t s) {
+  if (lanes_needed <= 1) return launch_staged<VEC, 1, 1, BWD>(a, part_size, s);
+  if (lanes_needed <= 2) return launch_staged<VEC, 2, 1, BWD>(a, part_size, s);
+  if (lanes_needed <= 4) return launch_staged<VEC, 4, 1, BWD>(a, part_size, s);
+  if (lanes_needed <= 8) return launch_staged<VEC, 4, 2, BWD>(a, part_size, s);
+  if (lanes_needed <= 12) return launch_staged<VEC, 4, 3, BWD>(a, part_size, s);
+  if (lanes_needed <= 16) return launch_staged<VEC, 4, 4, BWD>(a, part_size, s);
+  if (lanes_needed <= 32) return launch_staged<VEC, 4, 8, BWD>(a, part_size, s);
+  if (lanes_needed <= 64) return launch_staged<VEC, 8, 8, BWD>(a, part_size, s);
+  if (lanes_needed <= 128) return launch_staged<VEC, 16, 8, BWD>(a, part_size, s);
+  return launch_staged<VEC, 32, 8, BWD>(a, part_size, s);   // wider rows take several passes
 }
 
 template <bool BWD>
@@ -474,6 +383,10 @@ int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) 
   // with atomics, start from zero.
   EPP_CUDA_TRY(cudaMemsetAsync(a.out, 0, sizeof(float) * static_cast<size_t>(num_rows) * a.dim, s));
   if (a.num_parts == 0) return EPP_OK;
+  if (a.ld > 0x3fffffffLL) {
+    set_error("row stride too large");
+    return EPP_ERR_TOO_LARGE;
+  }
   // Widest gather: the lane's VEC floats must be aligned and inside the row stride.
   int vec = 1;
   if (a.ld % 4 == 0 && aligned(a.feat, 16) && a.ld >= ((a.dim + 3) / 4) * 4) vec = 4;
@@ -482,19 +395,10 @@ int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) 
   if (a.dim % 4 == 0 && aligned(a.out, 16)) a.ovec = 4;
   else if (a.dim % 2 == 0 && aligned(a.out, 8)) a.ovec = 2;
   const int lanes_needed = (a.dim + vec - 1) / vec;
-  int lpr = 1;
-  while (lpr < 32 && lpr < lanes_needed) lpr <<= 1;
-  if (spmm_kernel_choice() != 1) {
-    switch (vec) {
-      case 4:  return launch_staged_lpr<4, BWD>(a, lpr, part_size, s);
-      case 2:  return launch_staged_lpr<2, BWD>(a, lpr, part_size, s);
-      default: return launch_staged_lpr<1, BWD>(a, lpr, part_size, s);
-    }
-  }
   switch (vec) {
-    case 4:  return launch_lpr<4, BWD>(a, lpr, s);
-    case 2:  return launch_lpr<2, BWD>(a, lpr, s);
-    default: return launch_lpr<1, BWD>(a, lpr, s);
+    case 4:  return launch_shape<4, BWD>(a, lanes_needed, part_size, s);
+    case 2:  return launch_shape<2, BWD>(a, lanes_needed, part_size, s);
+    default: return launch_shape<1, BWD>(a, lanes_needed, part_size, s);
   }
 }
 

@@ -1,0 +1,100 @@
+"""Row-partition logic on two gloo ranks (CPU): ranges, shards, the row
+exchange, and the sharded execution-path preparation against the
+single-process oracle."""
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from eppgcn_b200 import dist as D
+from eppgcn_b200 import graphs
+from oracle import epp_oracle as O
+
+
+def free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def test_edge_balanced_ranges():
+    g = graphs.make_graph("pubmed", 0, cache=False)
+    for world in (1, 2, 3, 8):
+        b = D.edge_balanced_ranges(g.indptr, world)
+        assert b[0] == 0 and b[-1] == g.num_nodes and np.all(np.diff(b) >= 0) and len(b) == world + 1
+        edges = np.diff(g.indptr[b].astype(np.int64))
+        assert edges.sum() == g.num_edges
+        assert edges.max() - g.num_edges / world <= np.diff(g.indptr).max()     # off by at most one row
+    # a hub bigger than its share still leaves valid (possibly empty) ranges
+    hub = np.array([0, 100, 101, 102, 103], dtype=np.int32)
+    b = D.edge_balanced_ranges(hub, 4)
+    assert b[0] == 0 and b[-1] == 4 and np.all(np.diff(b) >= 0)
+
+
+def test_shards_tile_the_graph():
+    g = graphs.make_graph("cora", 0, cache=False)
+    b = D.edge_balanced_ranges(g.indptr, 3)
+    shards = [D.make_shard(g.indptr, g.indices, b, r) for r in range(3)]
+    assert sum(s.num_rows for s in shards) == g.num_nodes
+    assert np.array_equal(np.concatenate([s.indices for s in shards]), g.indices)
+    for s in shards:
+        assert s.indptr[0] == 0 and s.indptr[-1] == s.num_edges
+        assert np.array_equal(np.diff(s.indptr), np.diff(g.indptr[s.v0:s.v1 + 1]))
+
+
+def _worker(rank, world, port, results):
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        g = graphs.make_graph("cora", 0, cache=False)
+        n, e = g.num_nodes, g.num_edges
+        bounds = D.edge_balanced_ranges(g.indptr, world)
+        sh = D.make_shard(g.indptr, g.indices, bounds, rank)
+        # --- row exchange into a padded buffer -----------------------------------------
+        want = torch.arange(n * 22, dtype=torch.float32).reshape(n, 22)
+        full = torch.full((n, 24), -1.0)[:, :22]
+        D.all_gather_rows(full, want[sh.v0:sh.v1].clone(), bounds)
+        ok_gather = bool(torch.equal(full, want))
+        # --- sharded preparation: local marking + OR-reduced neighbour masks -----------
+        layers, ps, bs = 3, 4, 8
+        train = np.random.Generator(np.random.PCG64(7)).random(n) < 0.1
+        pp, p2n = O.build_part(ps, sh.indptr)
+        ngh = [torch.zeros(n, dtype=torch.bool) for _ in range(layers - 1)]
+        ems = [np.full(sh.num_edges, -1, dtype=np.int32) for _ in range(layers)]
+        nds = [np.zeros(n, dtype=np.int32) for _ in range(layers)]          # indexed by global row here
+        for i in range(layers):
+            src = train if i == 0 else ngh[i - 1].numpy()
+            dst = ngh[i].numpy() if i < layers - 1 else np.zeros(0, dtype=bool)
+            O.mask_forward(p2n.astype(np.int64) + sh.v0, pp, sh.indices, src, dst, ems[layers - 1 - i],
+                           nds[layers - 1 - i], layers, i + 1)
+            if i < layers - 1:
+                D.or_reduce_mask(ngh[i])
+        ref, ref_ngh = O.prepare_execution_path(g.indptr, g.indices, train, layers, ps, [bs] * layers)
+        e0, e1 = int(g.indptr[sh.v0]), int(g.indptr[sh.v1])
+        ok_prep = all(np.array_equal(ngh[i].numpy(), ref_ngh[i]) for i in range(layers - 1))
+        for i in range(layers):
+            ok_prep &= np.array_equal(ems[i], ref[i]["edge_mask"][e0:e1])
+            ok_prep &= np.array_equal(nds[i][sh.v0:sh.v1], ref[i]["node_degs"][sh.v0:sh.v1])
+            # the shard's compacted list is the matching slice of the global one
+            ids, cols, valid = O.compact_back_edge(ems[i], sh.indices)
+            before = int((ref[i]["edge_mask"][:e0] != -1).sum())
+            ok_prep &= np.array_equal(ids[:valid], ref[i]["id"][before:before + valid])
+            ok_prep &= np.array_equal(cols[:valid], ref[i]["edgeList"][before:before + valid])
+        # --- d_weight partials add up -----------------------------------------------------
+        part = torch.full((4, 3), float(rank + 1))
+        dist.all_reduce(part)
+        ok_sum = bool(torch.all(part == sum(range(1, world + 1))))
+        results[rank] = (ok_gather, bool(ok_prep), ok_sum)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_two_ranks_gloo():
+    world = 2
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, free_port(), results), nprocs=world, join=True)
+    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}

@@ -83,15 +83,15 @@ def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None)
     ld = full.stride(0)
     if full.stride(1) != 1 or ld < full.size(1):
         raise ValueError("full must have unit column stride")
-    works = []
-    for r in range(world):
-        a, b = int(bounds[r]), int(bounds[r + 1])
-        if b == a:
-            continue
-        # whole padded rows [a, b) are one contiguous block of the underlying buffer
-        block = torch.as_strided(full, (b - a, ld), (ld, 1), full.storage_offset() + a * ld)
-        works.append(dist.broadcast(block, src=dist.get_global_rank(group, r) if group else r,
-                                    group=group, async_op=True))
+    # whole padded rows [a, b) of a range are one contiguous block of the underlying buffer
+    blocks = [torch.as_strided(full, (int(bounds[r + 1]) - int(bounds[r]), ld), (ld, 1),
+                               full.storage_offset() + int(bounds[r]) * ld) for r in range(world)]
+    if dist.get_backend(group) == "nccl" and all(b.size(0) > 0 for b in blocks):
+        # uneven all-gather: NCCL runs the per-rank broadcasts as one group, all links busy at once
+        dist.all_gather(blocks, blocks[rank], group=group)
+        return full
+    works = [dist.broadcast(blocks[r], src=dist.get_global_rank(group, r) if group else r, group=group,
+                            async_op=True) for r in range(world) if blocks[r].size(0) > 0]
     for w in works:
         w.wait()
     return full

@@ -29,6 +29,7 @@ SIGNATURES = {
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
+    "eppgcn_compact_mask_static": (_I, [_P, _P, _P, _P, _I, _P, _P, _P]),
     "eppgcn_split_scratch_bytes": (_SZ, [_I]),
     "eppgcn_split_parts": (_I, [_P, _I, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
     "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
@@ -166,6 +167,19 @@ def compact_mask(edge_mask, col_idx, mode=0):
         counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
     valid, _ = _finish(counter)
     return out_id, out_edge, valid
+
+
+def compact_mask_static(edge_mask, col_idx, out_id, out_edge, counter):
+    """Compaction through the entry point that allocates nothing.  The caller
+    owns every buffer: ``out_id``/``out_edge`` (length of the input) and
+    ``counter`` (two int32: kept count, status).  Returns the kept count after
+    synchronising with the stream."""
+    check(lib().eppgcn_compact_mask_static(
+        _dev(edge_mask, torch.int32, "edge_mask"), _dev(col_idx, torch.int32, "column_index"),
+        _dev(out_id, torch.int32, "out_id"), _dev(out_edge, torch.int32, "out_edge"), edge_mask.numel(),
+        _dev(counter, torch.int32, "counter"), counter.data_ptr() + 4, _stream()))
+    valid, _ = _finish(counter)
+    return valid
 
 
 def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):

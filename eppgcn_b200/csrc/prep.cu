@@ -443,6 +443,81 @@ EPP_EXPORT int eppgcn_compact_mask(const int *edge_mask, const int *col_idx, int
   return EPP_OK;
 }
 
+// ---------------------------------------------------------------------------
+// Compaction without any allocation by anyone.
+//
+// Some hosts cannot give this library scratch memory at call time: a process
+// that handed the whole device to its own pool at start-up and runs without
+// headroom, a latency-critical thread that must never hit the device-wide
+// synchronisation cudaMalloc/cudaFree imply, or an embedding application that
+// forbids device allocation after initialisation.  For them the tile
+// descriptors of the single-pass scan live in this fixed array instead of a
+// caller-supplied buffer.  It is part of the library image: every GPU that
+// loads the library holds these bytes until the process exits.
+// ---------------------------------------------------------------------------
+constexpr int kStaticCompactMaxLength = 1 << 26;   // 67,108,864 edges
+constexpr size_t kStaticCompactBytes =
+    sizeof(epp::ScanHeader) + sizeof(unsigned long long) * (kStaticCompactMaxLength / epp::kCompactTile);   // 131,328 B
+static __device__ __align__(256) unsigned char g_static_compact_scratch[kStaticCompactBytes];
+
+// In host code `g_static_compact_scratch` is only a handle for the runtime, not
+// a device address; the address is looked up once per device, with that device
+// current, and cached.
+static int static_compact_scratch_address(void **ptr) {
+  constexpr int kMaxDevices = 64;
+  static void *cached[kMaxDevices] = {nullptr};
+  int dev = 0;
+  EPP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("device ordinal %d is beyond the %d devices this entry point tracks", dev, kMaxDevices);
+    return EPP_ERR_TOO_LARGE;
+  }
+  if (!cached[dev]) {
+    void *p = nullptr;
+    EPP_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_compact_scratch));
+    if (!p || reinterpret_cast<uintptr_t>(p) % 256 != 0) {
+      set_error("static scratch symbol resolved to an unusable address");
+      return EPP_ERR_CUDA;
+    }
+    cached[dev] = p;
+  }
+  *ptr = cached[dev];
+  return EPP_OK;
+}
+
+EPP_EXPORT int eppgcn_compact_mask_static(const int *edge_mask, const int *col_idx, int *out_id, int *out_edge,
+                                          int length, int *valid_len_dev, int *status_dev, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EPP_REQUIRE(length >= 0, "negative length");
+  EPP_REQUIRE(valid_len_dev && status_dev, "null result pointer");
+  if (length > kStaticCompactMaxLength) {
+    set_error("eppgcn_compact_mask_static handles at most %d edges per call, got %d; "
+              "use eppgcn_compact_mask with caller-provided scratch", kStaticCompactMaxLength, length);
+    return EPP_ERR_TOO_LARGE;
+  }
+  void *scratch = nullptr;
+  const int rc = static_compact_scratch_address(&scratch);
+  if (rc != EPP_OK) return rc;
+  EPP_CUDA_TRY(cudaMemsetAsync(valid_len_dev, 0, sizeof(int), s));
+  EPP_CUDA_TRY(cudaMemsetAsync(status_dev, 0, sizeof(int), s));
+  if (length == 0) return EPP_OK;
+  EPP_REQUIRE(edge_mask && col_idx && out_id && out_edge, "null pointer");
+  const int tiles = static_cast<int>(ceil_div_ll(length, kCompactTile));
+  ScanHeader *hdr = static_cast<ScanHeader *>(scratch);
+  unsigned long long *desc = reinterpret_cast<unsigned long long *>(hdr + 1);
+  // The array keeps the previous call's ticket, error word and descriptors:
+  // everything this call will read has to start from zero again.
+  EPP_CUDA_TRY(cudaMemsetAsync(scratch, 0, scan_scratch_bytes(tiles), s));
+  compact_mask_kernel<kLookback><<<tiles, kScanThreads, 0, s>>>(edge_mask, col_idx, out_id, out_edge, length,
+                                                                tiles, hdr, desc, valid_len_dev);
+  EPP_CHECK_LAUNCH("compact_mask_kernel<lookback, static scratch>");
+  zero_tail_kernel<<<tail_grid(length), 256, 0, s>>>(out_id, out_edge, valid_len_dev, 0, length);
+  EPP_CHECK_LAUNCH("zero_tail_kernel");
+  publish_status_kernel<<<1, 1, 0, s>>>(hdr, status_dev);
+  EPP_CHECK_LAUNCH("publish_status_kernel");
+  return EPP_OK;
+}
+
 EPP_EXPORT int eppgcn_split_parts(const int *node_deg, int num_nodes, int part_size, int *part_pointer,
                                   int out_len, void *scratch, size_t scratch_bytes, int *num_parts_dev,
                                   int *status_dev, int mode, void *stream) {

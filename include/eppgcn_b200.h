@@ -130,6 +130,37 @@ int eppgcn_compact_mask(const int *edge_mask, const int *col_idx,
                         int *valid_len_dev, int *status_dev, int mode, void *stream);
 
 /* ------------------------------------------------------------------------
+ * eppgcn_compact_mask for callers that cannot supply scratch memory.
+ * Has no counterpart in the reference (which calls cudaMalloc/cudaFree inside
+ * every compaction, EPPGCN/GCNConv/cuCompactor.cu:442-462).
+ *
+ * Same inputs, outputs and results as eppgcn_compact_mask in mode 0, but the
+ * scan's tile descriptors live in a fixed array inside the library instead of
+ * a caller buffer, and the call allocates nothing: no cudaMalloc, no cudaFree,
+ * no allocating library routine.  Meant for hosts that must not allocate on
+ * the device once they are running -- a process whose own pool already owns
+ * all device memory, a thread that cannot afford the device-wide
+ * synchronisation an allocation implies, an application that forbids
+ * allocation after start-up.
+ *
+ * Limits and rules:
+ *  - length <= 67,108,864 (2^26) edges; larger inputs return EPP_ERR_TOO_LARGE
+ *    and must use eppgcn_compact_mask.
+ *  - The array costs 131,328 bytes of device memory on every GPU that loads
+ *    the library, for the life of the process.
+ *  - The first call on a device looks up the array's device address (once per
+ *    device, with that device current).  Make that first call outside any
+ *    stream capture.
+ *  - All calls on a device share the one array.  Each call clears what it
+ *    needs, so calls issued back to back on one stream are fine; two calls
+ *    whose kernels can overlap on the GPU (different streams, no ordering)
+ *    race on it and give undefined results.
+ */
+int eppgcn_compact_mask_static(const int *edge_mask, const int *col_idx,
+                               int *out_id, int *out_edge, int length,
+                               int *valid_len_dev, int *status_dev, void *stream);
+
+/* ------------------------------------------------------------------------
  * Splitting the active rows into backward parts.
  * Replaces compact_part -> cuCompactor_part::compact followed by
  * exclusive_scan (EPPGCN/GCNConv/cuCompactor.cu:492-619, :42-48, :688-692).

@@ -26,6 +26,7 @@ SIGNATURES = {
     "eppgcn_last_error": (C.c_char_p, []),
     "eppgcn_spmm_forward": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_spmm_backward_compacted": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
@@ -97,10 +98,24 @@ def _row_stride(t: torch.Tensor, name: str) -> int:
     return t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
 
 
+def update_scaled(x, w, scale=None, pad_to=8):
+    """``scale[:, None] * (x @ w)`` as a view ``[N, dout]`` of a buffer whose
+    row stride is ``dout`` rounded up to ``pad_to`` floats."""
+    n, k = x.shape
+    dout = w.size(1)
+    ld = (dout + pad_to - 1) // pad_to * pad_to
+    full = torch.empty(n, ld, device=x.device, dtype=torch.float32)
+    check(lib().eppgcn_update_scaled(
+        full.data_ptr(), ld, x.data_ptr(), _row_stride(x, "x"), _dev(w, torch.float32, "w"),
+        None if scale is None else _dev(scale, torch.float32, "scale"), n, k, dout, _stream()))
+    return full[:, :dout]
+
+
 def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size=0, dim_worker=32,
-                 warp_per_block=8, out=None, deg_row=None):
+                 warp_per_block=8, out=None, deg_row=None, prescaled=False):
     """``out = diag(deg_row) A diag(degrees) feat`` over the CSR; ``feat`` may
-    have a padded row stride."""
+    have a padded row stride.  ``prescaled``: the rows of ``feat`` already carry
+    ``degrees[col]`` and the kernel skips that gather."""
     n = row_ptr.numel() - 1
     dim = feat.size(1)
     ld = _row_stride(feat, "feat")
@@ -110,7 +125,7 @@ def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size
     check(lib().eppgcn_spmm_forward(
         _dev(out, torch.float32, "out"), feat.data_ptr(), ld,
         _dev(row_ptr, torch.int32, "row_ptr"), _dev(col_idx, torch.int32, "col_idx"),
-        _dev(deg_row, torch.float32, "deg_row"), _dev(degrees, torch.float32, "degrees"),
+        _dev(deg_row, torch.float32, "deg_row"), None if prescaled else _dev(degrees, torch.float32, "degrees"),
         _dev(part_ptr, torch.int32, "part_ptr"), _dev(part2node, torch.int32, "part2node"),
         n, dim, part2node.numel(), part_size, dim_worker, warp_per_block, _stream()))
     return out

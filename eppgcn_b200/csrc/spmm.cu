@@ -88,6 +88,7 @@ struct GroupArgs {
   int num_parts;
   int dim;
   int ovec;                // widest aligned access into `out`: 4, 2 or 1 floats
+  int bwd;                 // 0: groups over a CSR (part2node), 1: parts over the compacted edge list (ids)
 };
 
 __device__ __forceinline__ void cp_async_4(int *smem_dst, const int *gmem_src) {
@@ -107,19 +108,18 @@ struct SetMeta {
   int lo, hi;          // row of the group before / after this one (-1 at either end of the list)
 };
 
-// BWD = false: groups (part_ptr, part2node) from build_part.  A row's groups are
+// bwd = 0: groups (part_ptr, part2node) from build_part.  A row's groups are
 //              consecutive, so a run of groups covers its whole row exactly when
 //              the groups on either side belong to other rows.
-// BWD = true : parts over the compacted edge list; the row of a part is
+// bwd = 1: parts over the compacted edge list; the row of a part is
 //              ids[part_ptr[p]], and the rows on either side are the ids of the
 //              edge before the part and of the edge after it.
-template <bool BWD>
 __device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, int g, int total_edges) {
   SetMeta m{0, 0, -1, -1, -1};
   if (g < a.num_parts) {
     m.beg = __ldg(a.part_ptr + g);
     m.end = __ldg(a.part_ptr + g + 1);
-    if (BWD) {
+    if (a.bwd) {
       if (m.end > m.beg) {
         m.row = __ldg(a.row_of + m.beg);
         m.lo = m.beg > 0 ? __ldg(a.row_of + m.beg - 1) : -1;
@@ -140,7 +140,7 @@ __device__ __forceinline__ SetMeta load_set_meta(const GroupArgs &a, int g, int 
 // did not fit its slab).  FULL: every sub-warp of the warp has all N edges and
 // every lane all T tiles, so nothing is tested.  `tiles` is the lane's bit mask
 // of tiles that hold feature columns.
-template <int VEC, int T, int N, bool FULL>
+template <int VEC, int T, int N, bool FULL, bool HASW>
 __device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, unsigned tiles, const char *fbytes,
                                              unsigned ld_bytes, unsigned tile_bytes, const float *deg_col,
                                              float (&acc)[T][VEC]) {
@@ -152,7 +152,7 @@ __device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, uns
 #pragma unroll
   for (int u = 0; u < N; ++u) {
     if (FULL || c[u] >= 0) {
-      w[u] = __ldg(deg_col + c[u]);
+      w[u] = HASW ? __ldg(deg_col + c[u]) : 1.f;
       const char *rowp = fbytes + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes;
 #pragma unroll
       for (int k = 0; k < T; ++k) {
@@ -176,13 +176,14 @@ __device__ __forceinline__ void gather_batch(const int *cs, int i0, int len, uns
 #pragma unroll
     for (int k = 0; k < T; ++k)
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) acc[k][i] = fmaf(w[u], v[u][k][i], acc[k][i]);
+      for (int i = 0; i < VEC; ++i)
+        acc[k][i] = HASW ? fmaf(w[u], v[u][k][i], acc[k][i]) : acc[k][i] + v[u][k][i];   // rows beyond len are zero
 }
 
 // One launch covers feature columns [0, min(dim_left, VEC*LPR*T)) of the
 // pointers it is given; wider rows are handled by the host with further
 // launches on shifted pointers.
-template <int VEC, int LPR, int T, bool BWD>
+template <int VEC, int LPR, int T, bool HASW>
 __global__ void __launch_bounds__(256, (T <= 4 ? 3 : 2))
 staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int col_aligned) {
   constexpr int G = kWarp / LPR;               // groups per set
@@ -231,8 +232,8 @@ staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int 
     return sbeg;
   };
 
-  SetMeta m0 = load_set_meta<BWD>(a, set * G + sub, total_edges);
-  SetMeta m1 = load_set_meta<BWD>(a, set + stride < nsets ? (set + stride) * G + sub : a.num_parts, total_edges);
+  SetMeta m0 = load_set_meta(a, set * G + sub, total_edges);
+  SetMeta m1 = load_set_meta(a, set + stride < nsets ? (set + stride) * G + sub : a.num_parts, total_edges);
   int base0 = stage(m0, slab0);
   cp_async_commit();
   float wr0 = m0.row >= 0 ? __ldg(a.deg_row + m0.row) : 0.f;
@@ -240,7 +241,7 @@ staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int 
 
   for (; set < nsets; set += stride) {
     const int set2 = set + 2 * stride;
-    const SetMeta m2 = load_set_meta<BWD>(a, set2 < nsets ? set2 * G + sub : a.num_parts, total_edges);
+    const SetMeta m2 = load_set_meta(a, set2 < nsets ? set2 * G + sub : a.num_parts, total_edges);
     const int base1 = stage(m1, slab0 + (cur ^ 1) * slab);
     cp_async_commit();
     const float wr1 = m1.row >= 0 ? __ldg(a.deg_row + m1.row) : 0.f;
@@ -261,21 +262,21 @@ staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int 
     int i0 = 0;
 #pragma unroll 1
     for (; i0 + U <= minlen; i0 += U)
-      gather_batch<VEC, T, U, true>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      gather_batch<VEC, T, U, true, HASW>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
 #pragma unroll 1
     for (; i0 + U <= maxlen; i0 += U)
-      gather_batch<VEC, T, U, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      gather_batch<VEC, T, U, false, HASW>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
     // warp-uniform tail: 4 + 2 + 1 covers any remainder below 8
     if (U > 4 && maxlen - i0 >= 4) {
-      gather_batch<VEC, T, 4, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      gather_batch<VEC, T, 4, false, HASW>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
       i0 += 4;
     }
     if (U > 2 && maxlen - i0 >= 2) {
-      gather_batch<VEC, T, 2, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      gather_batch<VEC, T, 2, false, HASW>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
       i0 += 2;
     }
     if (U > 1 && maxlen - i0 >= 1)
-      gather_batch<VEC, T, 1, false>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
+      gather_batch<VEC, T, 1, false, HASW>(cs, i0, len, tiles, fbytes, ld_bytes, tile_bytes, a.deg_col, acc);
 #pragma unroll
     for (int k = 0; k < T; ++k)
 #pragma unroll
@@ -325,7 +326,7 @@ struct LaunchInfo {
   int num_sms = 0;
 };
 
-template <int VEC, int LPR, int T, bool BWD>
+template <int VEC, int LPR, int T, bool HASW>
 int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
   constexpr int G = kWarp / LPR;
   constexpr int SPAN = VEC * LPR * T;           // feature columns per launch
@@ -339,10 +340,10 @@ int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
     EPP_CUDA_TRY(cudaGetDevice(&dev));
     EPP_CUDA_TRY(cudaDeviceGetAttribute(&info.num_sms, cudaDevAttrMultiProcessorCount, dev));
     if (smem > 48 * 1024)
-      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, T, BWD>,
+      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, T, HASW>,
                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&info.blocks_per_sm,
-                                                               staged_spmm_kernel<VEC, LPR, T, BWD>, 256, smem));
+                                                               staged_spmm_kernel<VEC, LPR, T, HASW>, 256, smem));
     if (info.blocks_per_sm < 1) info.blocks_per_sm = 1;
     info.smem = smem;
   }
@@ -356,28 +357,28 @@ int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
     a.feat = a0.feat + col0;
     a.out = a0.out + col0;
     const int cols = a0.dim - col0 < SPAN ? a0.dim - col0 : SPAN;
-    staged_spmm_kernel<VEC, LPR, T, BWD><<<static_cast<unsigned>(blocks), 256, smem, s>>>(a, cols, slab, col_aligned);
+    staged_spmm_kernel<VEC, LPR, T, HASW><<<static_cast<unsigned>(blocks), 256, smem, s>>>(a, cols, slab, col_aligned);
     EPP_CHECK_LAUNCH("staged_spmm_kernel");
   }
   return EPP_OK;
 }
 
 // Lanes per row and tiles per lane for a row of `lanes_needed` VEC-wide pieces.
-template <int VEC, bool BWD>
+template <int VEC, bool HASW>
 int launch_shape(const GroupArgs &a, int lanes_needed, int part_size, cudaStream_t s) {
-  if (lanes_needed <= 1) return launch_staged<VEC, 1, 1, BWD>(a, part_size, s);
-  if (lanes_needed <= 2) return launch_staged<VEC, 2, 1, BWD>(a, part_size, s);
-  if (lanes_needed <= 4) return launch_staged<VEC, 4, 1, BWD>(a, part_size, s);
-  if (lanes_needed <= 8) return launch_staged<VEC, 4, 2, BWD>(a, part_size, s);
-  if (lanes_needed <= 12) return launch_staged<VEC, 4, 3, BWD>(a, part_size, s);
-  if (lanes_needed <= 16) return launch_staged<VEC, 4, 4, BWD>(a, part_size, s);
-  if (lanes_needed <= 32) return launch_staged<VEC, 4, 8, BWD>(a, part_size, s);
-  if (lanes_needed <= 64) return launch_staged<VEC, 8, 8, BWD>(a, part_size, s);
-  if (lanes_needed <= 128) return launch_staged<VEC, 16, 8, BWD>(a, part_size, s);
-  return launch_staged<VEC, 32, 8, BWD>(a, part_size, s);   // wider rows take several passes
+  if (lanes_needed <= 1) return launch_staged<VEC, 1, 1, HASW>(a, part_size, s);
+  if (lanes_needed <= 2) return launch_staged<VEC, 2, 1, HASW>(a, part_size, s);
+  if (lanes_needed <= 4) return launch_staged<VEC, 4, 1, HASW>(a, part_size, s);
+  if (lanes_needed <= 8) return launch_staged<VEC, 4, 2, HASW>(a, part_size, s);
+  if (lanes_needed <= 12) return launch_staged<VEC, 4, 3, HASW>(a, part_size, s);
+  if (lanes_needed <= 16) return launch_staged<VEC, 4, 4, HASW>(a, part_size, s);
+  if (lanes_needed <= 32) return launch_staged<VEC, 4, 8, HASW>(a, part_size, s);
+  if (lanes_needed <= 64) return launch_staged<VEC, 8, 8, HASW>(a, part_size, s);
+  if (lanes_needed <= 128) return launch_staged<VEC, 16, 8, HASW>(a, part_size, s);
+  return launch_staged<VEC, 32, 8, HASW>(a, part_size, s);   // wider rows take several passes
 }
 
-template <bool BWD>
+template <bool HASW>
 int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) {
   // Dense result: rows that no group touches, and rows that are accumulated
   // with atomics, start from zero.
@@ -396,9 +397,9 @@ int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) 
   else if (a.dim % 2 == 0 && aligned(a.out, 8)) a.ovec = 2;
   const int lanes_needed = (a.dim + vec - 1) / vec;
   switch (vec) {
-    case 4:  return launch_shape<4, BWD>(a, lanes_needed, part_size, s);
-    case 2:  return launch_shape<2, BWD>(a, lanes_needed, part_size, s);
-    default: return launch_shape<1, BWD>(a, lanes_needed, part_size, s);
+    case 4:  return launch_shape<4, HASW>(a, lanes_needed, part_size, s);
+    case 2:  return launch_shape<2, HASW>(a, lanes_needed, part_size, s);
+    default: return launch_shape<1, HASW>(a, lanes_needed, part_size, s);
   }
 }
 
@@ -416,13 +417,14 @@ EPP_EXPORT int eppgcn_spmm_forward(float *out, const float *feat, long long feat
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(feat_ld >= dim, "feat_ld must be >= dim");
   if (num_nodes == 0) return EPP_OK;
-  EPP_REQUIRE(out && feat && row_ptr && deg_row && deg_col, "null pointer");
+  EPP_REQUIRE(out && feat && row_ptr && deg_row, "null pointer");
   EPP_REQUIRE(num_parts == 0 || (col_idx && part_ptr && part2node), "null pointer");
   epp::GroupArgs a{};
   a.out = out; a.feat = feat; a.ld = feat_ld;
   a.part_ptr = part_ptr; a.row_of = part2node; a.row_ptr = row_ptr; a.col = col_idx;
-  a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim;
-  return epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
+  a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim; a.bwd = 0;
+  return deg_col ? epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream))
+                 : epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
 }
 
 EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
@@ -435,11 +437,12 @@ EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, l
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(d_out_ld >= dim, "d_out_ld must be >= dim");
   if (num_nodes == 0) return EPP_OK;
-  EPP_REQUIRE(d_in && d_out && deg_row && deg_col, "null pointer");
+  EPP_REQUIRE(d_in && d_out && deg_row, "null pointer");
   EPP_REQUIRE(num_parts == 0 || (ids && part_ptr && edge_list), "null pointer");
   epp::GroupArgs a{};
   a.out = d_in; a.feat = d_out; a.ld = d_out_ld;
   a.part_ptr = part_ptr; a.row_of = ids; a.row_ptr = nullptr; a.col = edge_list;
-  a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim;
-  return epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
+  a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim; a.bwd = 1;
+  return deg_col ? epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream))
+                 : epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
 }

@@ -156,7 +156,7 @@ class DistHotPath:
 
     def forward(self, feat_full, out_local):
         return self.capi.spmm_forward(feat_full, self.row, self.col, self.deg, self.pp, self.p2n, self.part_size,
-                                      out=out_local, deg_row=self.deg_row)
+                                      out=out_local, deg_row=self.deg_row, prescaled=True)
 
     def backward(self, i, d_out_full, out_local):
         p = self.path[i]

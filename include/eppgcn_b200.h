@@ -52,6 +52,10 @@ const char *eppgcn_last_error(void);
  * deg_row / deg_col   per-vertex factors of the destination and the source
  *           side.  The reference passes one `degrees` array for both; a
  *           row-partitioned caller passes `degrees + first_row` as deg_row.
+ *           deg_col may be NULL: the rows of feat then already carry their
+ *           source-side factor (see eppgcn_update_scaled) and the kernel
+ *           computes deg_row[r] * sum feat[col_idx[e]][:], one 32-byte sector
+ *           less per edge.
  * part_ptr  [num_parts+1], part2node [num_parts]: the neighbour groups of
  *           build_part -- consecutive, non-overlapping, covering every row.
  * part_size, dim_worker, warp_per_block: the reference's launch knobs
@@ -81,6 +85,7 @@ int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
  *           compacted edges [part_ptr[p], part_ptr[p+1]) of one row.
  * part_size, blockx, blocky: reference knobs (EPPGCN/param.py:6-24,182-200),
  *           accepted for parity; the result does not depend on them.
+ * deg_col may be NULL with the same meaning as in eppgcn_spmm_forward.
  */
 int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
                                    const int *ids, const int *part_ptr, const int *edge_list,
@@ -88,6 +93,24 @@ int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_
                                    int num_nodes, int dim, int num_parts,
                                    int part_size, int blockx, int blocky,
                                    void *stream);
+
+/* ------------------------------------------------------------------------
+ * Dense update of a layer with the source-side factor folded in.
+ * Replaces the torch::mm(input, weight) of the forward wrapper
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:142) for narrow outputs.
+ *
+ *   out[r][c] = scale[r] * sum_k x[r][k] * w[k][c]        c < dout <= 32
+ *
+ * FP32 FMA on the CUDA cores (no reduced-precision tensor-core path).
+ * x    [num_rows] rows of stride ldx floats, w [k][dout] dense row-major,
+ * out  rows of stride ld_out floats (ld_out >= dout); columns dout..ld_out-1
+ *      of a padded row are written with zeros when ld_out covers them.
+ * scale may be NULL (plain x @ w).  x and out rows must be 16-byte aligned
+ * (strides multiples of 4 floats).  dout > 32 returns EPP_ERR_TOO_LARGE.
+ */
+int eppgcn_update_scaled(float *out, long long ld_out, const float *x, long long ldx,
+                         const float *w, const float *scale,
+                         int num_rows, int k, int dout, void *stream);
 
 /* ------------------------------------------------------------------------
  * Execution-path marking for one preparation step.

@@ -127,3 +127,49 @@ def test_backward_train_ratios(cuda, ratio):
         assert_close(out.cpu().numpy(), want, what=f"backward ratio {ratio}")
         off_path = conv["node_degs"] == 0
         assert np.all(out.cpu().numpy()[off_path] == 0), "rows off the path must come back zero"
+
+
+@pytest.mark.parametrize("n,k,dout", [(1, 1, 1), (127, 3, 4), (128, 12, 16), (129, 96, 16), (1000, 128, 22),
+                                      (333, 130, 32), (2049, 16, 22), (64, 7, 5)])
+@pytest.mark.parametrize("scaled", [True, False])
+def test_update_scaled(cuda, n, k, dout, scaled):
+    """diag(scale) (X W) with FP32 FMA against float64; K-long fp32 dot products."""
+    rng = np.random.Generator(np.random.PCG64(n + k + dout))
+    kp = (k + 3) // 4 * 4
+    x_full = torch.full((n, kp), float("nan"), device=cuda)                  # row stride padded to 16 bytes
+    x = rng.standard_normal((n, k)).astype(np.float32)
+    x_full[:, :k] = t(x, cuda)
+    w = rng.uniform(-0.5, 0.5, (k, dout)).astype(np.float32)
+    s = rng.uniform(0.1, 2.0, n).astype(np.float32)
+    got = capi.update_scaled(x_full[:, :k], t(w, cuda), t(s, cuda) if scaled else None)
+    assert got.shape == (n, dout) and got.stride(0) % 8 == 0
+    want = x.astype(np.float64) @ w.astype(np.float64)
+    if scaled:
+        want *= s.astype(np.float64)[:, None]
+    mag = np.abs(x.astype(np.float64)) @ np.abs(w.astype(np.float64)) * (s[:, None] if scaled else 1.0)
+    err = np.abs(got.cpu().numpy() - want)
+    assert np.all(err <= 1e-6 + 4e-7 * mag * max(1, int(np.sqrt(k)))), f"worst {err.max():.3e}"
+    pad = got.stride(0) - dout
+    if pad:                                                                   # padding columns are zeroed
+        full = torch.as_strided(got, (n, got.stride(0)), (got.stride(0), 1))
+        assert torch.count_nonzero(full[:, dout:]).item() == 0
+
+
+def test_update_rejects_wide_outputs(cuda):
+    with pytest.raises(capi.EppError) as e:
+        capi.update_scaled(torch.zeros(8, 8, device=cuda), torch.zeros(8, 33, device=cuda))
+    assert e.value.status == capi.EPP_ERR_TOO_LARGE
+
+
+@pytest.mark.parametrize("dim", [1, 16, 22, 64, 128])
+def test_forward_prescaled_rows(cuda, dim):
+    """deg_col = NULL: rows that already carry deg[col] give the same result."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    feat = np.random.Generator(np.random.PCG64(dim)).standard_normal((n, dim)).astype(np.float32)
+    pp, p2n = O.build_part(6, indptr)
+    scaled = t(feat * deg[:, None], cuda)
+    got = capi.spmm_forward(scaled, t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda), t(p2n, cuda), 6,
+                            prescaled=True)
+    assert_close(got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), 2e-5, 2e-6, f"prescaled dim {dim}")

@@ -393,6 +393,8 @@ def main():
     p.add_argument("--workload", default="rmat21")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--backsize", type=int, default=32)
+    p.add_argument("--exchange", default="balanced", choices=["balanced", "allgather", "halo"],
+                   help="multi-GPU partition/exchange, see eppgcn_b200.dist.DistHotPath")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-full-epoch", action="store_true")
     p.add_argument("--kernels-only", action="store_true",

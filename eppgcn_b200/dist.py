@@ -66,6 +66,45 @@ def make_shard(indptr: np.ndarray, indices: np.ndarray, bounds: np.ndarray, rank
     return RowShard(rank, v0, v1, local, np.ascontiguousarray(indices[e0:e1]))
 
 
+def balanced_relabel(indptr: np.ndarray, world: int):
+    """Vertex relabelling that gives every rank the same number of rows AND
+    about the same number of edges: vertices sorted by degree are dealt to the
+    ranks round-robin; rank ``g`` owns new ids ``[g*n_loc, (g+1)*n_loc)``.
+
+    Equal row counts let the row exchange be one plain NCCL all-gather (2.3x
+    faster here than the grouped broadcasts uneven blocks need), and dealing
+    the hubs out evens the local work.  Returns ``(new_of_old[N], n_loc)``;
+    new ids ``>= N`` up to ``world*n_loc`` are padding rows without edges.
+    """
+    deg = np.diff(np.asarray(indptr, dtype=np.int64))
+    n = deg.shape[0]
+    n_loc = -(-n // world)
+    order = np.argsort(-deg, kind="stable")
+    i = np.arange(n, dtype=np.int64)
+    new_of_old = np.empty(n, dtype=np.int64)
+    new_of_old[order] = (i % world) * n_loc + i // world
+    return new_of_old, n_loc
+
+
+def make_relabelled_shard(indptr: np.ndarray, indices: np.ndarray, new_of_old: np.ndarray, n_loc: int,
+                          rank: int, world: int) -> RowShard:
+    """Rank ``rank``'s rows of the relabelled graph: local row pointers, column
+    ids in the new numbering (rows keep their edges' original order)."""
+    n = indptr.shape[0] - 1
+    old_of_new = np.full(n_loc * world, -1, dtype=np.int64)
+    old_of_new[new_of_old] = np.arange(n, dtype=np.int64)
+    mine = old_of_new[rank * n_loc:(rank + 1) * n_loc]
+    valid = mine >= 0
+    safe = np.where(valid, mine, 0)
+    lens = np.where(valid, indptr[safe + 1].astype(np.int64) - indptr[safe], 0)
+    local = np.zeros(n_loc + 1, dtype=np.int64)
+    np.cumsum(lens, out=local[1:])
+    starts = np.repeat(indptr[safe].astype(np.int64) - local[:-1], lens)
+    src = starts + np.arange(int(local[-1]), dtype=np.int64)
+    cols = new_of_old[indices[src]].astype(np.int32)
+    return RowShard(rank, rank * n_loc, (rank + 1) * n_loc, local.astype(np.int32), cols)
+
+
 def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None):
     """Fills ``full[b[r]:b[r+1]]`` on every rank with rank ``r``'s ``local``
     rows.  Row counts differ between ranks, so the exchange is one broadcast
@@ -77,8 +116,8 @@ def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None)
     v0, v1 = int(bounds[rank]), int(bounds[rank + 1])
     if local.size(0) != v1 - v0:
         raise ValueError("local rows do not match this rank's range")
-    full[v0:v1, :d].copy_(local)
     if world == 1:
+        full[v0:v1, :d].copy_(local)
         return full
     ld = full.stride(0)
     if full.stride(1) != 1 or ld < full.size(1):
@@ -86,6 +125,17 @@ def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None)
     # whole padded rows [a, b) of a range are one contiguous block of the underlying buffer
     blocks = [torch.as_strided(full, (int(bounds[r + 1]) - int(bounds[r]), ld), (ld, 1),
                                full.storage_offset() + int(bounds[r]) * ld) for r in range(world)]
+    if all(b.size(0) == blocks[0].size(0) for b in blocks) and full.size(0) == world * blocks[0].size(0) \
+            and dist.get_backend(group) == "nccl":
+        # equal blocks: one plain all-gather over the whole padded buffer
+        whole = torch.as_strided(full, (full.size(0), ld), (ld, 1), full.storage_offset())
+        mine = _padded_rows(local)
+        if mine.size(1) != ld or not mine.is_contiguous():      # different padding: go through the own block
+            full[v0:v1, :d].copy_(local)
+            mine = blocks[rank]
+        dist.all_gather_into_tensor(whole, mine, group=group)
+        return full
+    full[v0:v1, :d].copy_(local)
     if dist.get_backend(group) == "nccl" and all(b.size(0) > 0 for b in blocks):
         # uneven all-gather: NCCL runs the per-rank broadcasts as one group, all links busy at once
         dist.all_gather(blocks, blocks[rank], group=group)
@@ -105,18 +155,142 @@ def or_reduce_mask(mask: torch.Tensor, group=None):
     return mask
 
 
-class DistHotPath:
-    """One rank's device state: CSR shard, groups, prepared execution path."""
+def _padded_rows(t: torch.Tensor) -> torch.Tensor:
+    """The whole rows (row stride wide) behind a ``[n, d]`` view with unit column stride."""
+    if t.dim() != 2 or (t.size(1) > 1 and t.stride(1) != 1):
+        raise ValueError("expected a 2-D tensor with unit column stride")
+    ld = t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
+    return t if ld == t.size(1) else torch.as_strided(t, (t.size(0), ld), (ld, 1), t.storage_offset())
 
-    def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None):
+
+class HaloPlan:
+    """Exchange of only the source rows a rank's edges reference.
+
+    ``cols`` holds global source ids (one per edge).  The distinct ids, sorted,
+    define the rank's compact source buffer; because every owner's range is a
+    contiguous id interval, that order is also "grouped by owner", so one
+    all-to-all with per-owner row counts fills the buffer in place.  ``remap``
+    gives every edge its position in the buffer and replaces the global column
+    ids in the kernels' arguments.  Built once per aggregation (forward: all
+    local edges; backward of a layer: the compacted edges of its path).
+    """
+
+    def __init__(self, cols: torch.Tensor, bounds, rank: int, world: int, group=None):
+        dev = cols.device
+        self.rank, self.world, self.group = rank, world, group
+        ids = cols.long()
+        self.needed = torch.unique(ids)                                    # sorted global ids
+        self.remap = torch.searchsorted(self.needed, ids).to(torch.int32)
+        b = torch.as_tensor(np.asarray(bounds, dtype=np.int64), device=dev)
+        cut = torch.searchsorted(self.needed, b)                           # owner r: needed[cut[r]:cut[r+1]]
+        self.recv_counts = (cut[1:] - cut[:-1]).tolist()
+        owner = torch.bucketize(self.needed, b[1:], right=True)
+        request = self.needed - b[owner]                                   # row ids local to their owner
+        counts_in = torch.tensor(self.recv_counts, dtype=torch.int64, device=dev)
+        counts_out = torch.empty_like(counts_in)
+        if world > 1:
+            dist.all_to_all_single(counts_out, counts_in, group=group)
+        else:
+            counts_out.copy_(counts_in)
+        self.send_counts = counts_out.tolist()
+        self.send_idx = torch.empty(int(sum(self.send_counts)), dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_to_all_single(self.send_idx, request, self.send_counts, self.recv_counts, group=group)
+        else:
+            self.send_idx.copy_(request)
+        self.num_rows = int(self.needed.numel())
+
+    def exchange(self, local: torch.Tensor) -> torch.Tensor:
+        """``local``: this rank's rows ``[n_local, d]`` (row stride may be
+        padded).  Returns the compact source buffer ``[num_rows, d]`` with the
+        same row stride, row ``k`` holding global row ``needed[k]``."""
+        rows = _padded_rows(local)
+        send = rows.index_select(0, self.send_idx)
+        if self.world == 1:
+            return send[:, :local.size(1)]
+        buf = torch.empty(self.num_rows, rows.size(1), dtype=local.dtype, device=local.device)
+        dist.all_to_all_single(buf, send, self.recv_counts, self.send_counts, group=self.group)
+        return buf[:, :local.size(1)]
+
+
+class MaskedGather:
+    """Exchange of the rows selected by a vertex mask that every rank holds
+    (the source mask of a backward layer: only those rows of ``d_output`` are
+    ever read).  For equal row blocks per rank.  Rank ``g``'s selected rows are
+    packed into ``cap`` slots (the largest per-rank count), so the exchange is
+    one plain all-gather of ``world * cap`` rows; ``pos`` maps a vertex id to
+    its slot and replaces the column ids in the kernel's arguments."""
+
+    def __init__(self, mask: torch.Tensor, n_loc: int, rank: int, world: int, group=None):
+        self.rank, self.world, self.group = rank, world, group
+        blocks = mask.view(world, n_loc)
+        counts = blocks.sum(1)
+        self.cap = max(int(counts.max().item()), 1)
+        within = torch.cumsum(blocks, 1, dtype=torch.int64) - 1
+        slot = torch.arange(world, device=mask.device, dtype=torch.int64)[:, None] * self.cap + within
+        self.pos = torch.where(blocks, slot, torch.zeros_like(slot)).view(-1).to(torch.int32)
+        self.send_idx = torch.nonzero(blocks[rank]).view(-1)
+        self.count = int(self.send_idx.numel())
+        self.num_rows = world * self.cap
+        self.selected = torch.nonzero(mask).view(-1)            # vertex ids, in slot order per rank
+
+    def compact(self, per_vertex: torch.Tensor, fill=0) -> torch.Tensor:
+        """A per-vertex array rearranged into slot order."""
+        out = torch.full((self.num_rows,), fill, dtype=per_vertex.dtype, device=per_vertex.device)
+        out[self.pos[self.selected].long()] = per_vertex[self.selected]
+        return out
+
+    def exchange(self, local: torch.Tensor) -> torch.Tensor:
+        rows = _padded_rows(local)
+        send = torch.empty(self.cap, rows.size(1), dtype=local.dtype, device=local.device)
+        if self.count:
+            torch.index_select(rows, 0, self.send_idx, out=send[:self.count])
+        if self.world == 1:
+            return send[:, :local.size(1)]
+        buf = torch.empty(self.num_rows, rows.size(1), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(buf, send, group=self.group)
+        return buf[:, :local.size(1)]
+
+
+class DistHotPath:
+    """One rank's device state: CSR shard, groups, prepared execution path and
+    the exchange plans.  ``exchange``:
+
+    ``"balanced"``   (default) vertices relabelled so that every rank owns the same
+                     number of rows and about the same number of edges; the row
+                     exchange is one plain NCCL all-gather.
+    ``"allgather"``  contiguous id ranges with equal edge counts, uneven blocks
+                     (grouped broadcasts).
+    ``"halo"``       same ranges, only referenced rows travel (all-to-all); least
+                     bytes, but NCCL send/recv was the slowest of the three on
+                     8 x B200 for this graph.
+    """
+
+    def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None,
+                 exchange: str = "balanced"):
         import eppgcn_b200
         from eppgcn_b200 import capi
         self.capi, self.dev, self.rank, self.world, self.group = capi, dev, rank, world, group
+        self.mode = exchange
         gnna = eppgcn_b200.load_gnnadvisor()
         g = ds.graph
-        self.n = g.num_nodes
-        self.bounds = edge_balanced_ranges(g.indptr, world)
-        sh = make_shard(g.indptr, g.indices, self.bounds, rank)
+        degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
+        if exchange == "balanced":
+            # relabelled graph: equal rows per rank, hubs dealt out; every per-vertex array follows the new ids
+            self.new_of_old, n_loc = balanced_relabel(g.indptr, world)
+            self.n = n_loc * world
+            self.bounds = np.arange(world + 1, dtype=np.int64) * n_loc
+            sh = make_relabelled_shard(g.indptr, g.indices, self.new_of_old, n_loc, rank, world)
+            deg_new = np.ones(self.n, dtype=np.float32)
+            deg_new[self.new_of_old] = degrees_np
+            train_new = np.zeros(self.n, dtype=bool)
+            train_new[self.new_of_old] = train_np
+            degrees_np, train_np = deg_new, train_new
+        else:
+            self.new_of_old = None
+            self.n = g.num_nodes
+            self.bounds = edge_balanced_ranges(g.indptr, world)
+            sh = make_shard(g.indptr, g.indices, self.bounds, rank)
         self.shard = sh
         self.part_size = max(int(ds.avg_degree), 1)
         L = ds.num_layers
@@ -124,10 +298,10 @@ class DistHotPath:
         pp, p2n = gnna.build_part(self.part_size, row_cpu)
         self.row, self.col = row_cpu.to(dev), torch.from_numpy(sh.indices).to(dev)
         self.pp, self.p2n = pp.to(dev), p2n.to(dev)
-        self.deg = ds.degrees.to(dev)
+        self.deg = torch.from_numpy(degrees_np).to(dev)
         self.deg_row = self.deg[sh.v0:sh.v1]
         n_loc, e_loc = sh.num_rows, sh.num_edges
-        train = ds.train_mask.to(dev)
+        train = torch.from_numpy(train_np).to(dev)
         ngh = [torch.zeros(self.n, dtype=torch.bool, device=dev) for _ in range(L - 1)]
         edge_masks = [torch.full((e_loc,), -1, dtype=torch.int32, device=dev) for _ in range(L)]
         node_degs = [torch.zeros(n_loc, dtype=torch.int32, device=dev) for _ in range(L)]
@@ -150,17 +324,54 @@ class DistHotPath:
         self.prep_s = time.perf_counter() - t0
         self.ngh_masks, self.node_degs, self.edge_masks = ngh, node_degs, edge_masks
         self.back_size = back_size
+        if exchange == "balanced":
+            # a backward layer reads d_output only on its step's source mask: exchange just those rows
+            t0 = time.perf_counter()
+            for j, p in enumerate(self.path):
+                step = L - 1 - j
+                src = train if step == 0 else ngh[step - 1]
+                plan = MaskedGather(src, n_loc, rank, world, group)
+                edges_c = torch.zeros_like(p["edges"])
+                edges_c[:p["valid"]] = plan.pos[p["edges"][:p["valid"]].long()]
+                p.update(plan=plan, edges_c=edges_c, deg_c=plan.compact(self.deg, 0.0))
+            torch.cuda.synchronize(dev)
+            self.plan_s = time.perf_counter() - t0
+        if exchange == "halo":
+            t0 = time.perf_counter()
+            self.fwd_plan = HaloPlan(self.col, self.bounds, rank, world, group)
+            self.col_c = self.fwd_plan.remap
+            for p in self.path:
+                plan = HaloPlan(p["edges"][:p["valid"]], self.bounds, rank, world, group)
+                edges_c = torch.zeros_like(p["edges"])
+                edges_c[:p["valid"]] = plan.remap
+                p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.needed].contiguous())
+            torch.cuda.synchronize(dev)
+            self.plan_s = time.perf_counter() - t0
 
     def gather(self, full, local):
         return all_gather_rows(full, local, self.bounds, self.group)
 
     def forward(self, feat_full, out_local):
+        """Local forward aggregation over a whole-graph source matrix (pre-scaled rows)."""
         return self.capi.spmm_forward(feat_full, self.row, self.col, self.deg, self.pp, self.p2n, self.part_size,
                                       out=out_local, deg_row=self.deg_row, prescaled=True)
 
     def backward(self, i, d_out_full, out_local):
         p = self.path[i]
         return self.capi.spmm_backward_compacted(d_out_full, p["id"], p["pp"], p["edges"], self.deg, p["parts"],
+                                                 self.back_size, out=out_local, deg_row=self.deg_row,
+                                                 num_rows=self.shard.num_rows)
+
+    def forward_halo(self, local, out_local):
+        """Exchange of the referenced (pre-scaled) source rows, then the local forward aggregation."""
+        buf = self.fwd_plan.exchange(local)
+        return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
+                                      out=out_local, deg_row=self.deg_row, prescaled=True)
+
+    def backward_halo(self, i, d_out_local, out_local):
+        p = self.path[i]
+        buf = p["plan"].exchange(d_out_local)
+        return self.capi.spmm_backward_compacted(buf, p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
                                                  self.back_size, out=out_local, deg_row=self.deg_row,
                                                  num_rows=self.shard.num_rows)
 
@@ -180,22 +391,53 @@ def run_bench(args, rank: int, world: int, dev):
         ds = graphs.load_workload(args.workload, args.seed)
     n, e = ds.num_nodes, ds.num_edges
     dims = [spec["hidden"], spec["classes"]]
-    hp = DistHotPath(ds, dev, rank, world, args.backsize)
+    mode = getattr(args, "exchange", "balanced")
+    halo = mode == "halo"
+    hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode)
     n_loc = hp.shard.num_rows
     gen = torch.Generator(device=dev).manual_seed(args.seed + rank)
     widths = (dims[0], dims[1], dims[1], dims[0])
-    local_in = [torch.randn(n_loc, d, device=dev, generator=gen) for d in widths]
-    full = [B.padded(n, dims[0], dev, gen), B.padded(n, dims[1], dev, gen),
-            torch.empty(n, dims[1], device=dev), torch.empty(n, dims[0], device=dev)]
+    # forward inputs as the update step leaves them (padded rows), backward inputs as autograd does (dense)
+    local_in = [B.padded(n_loc, dims[0], dev, gen), B.padded(n_loc, dims[1], dev, gen),
+                torch.randn(n_loc, dims[1], device=dev, generator=gen),
+                torch.randn(n_loc, dims[0], device=dev, generator=gen)]
     outs = [torch.empty(n_loc, d, device=dev) for d in widths]
+    if halo:
+        plans = [hp.fwd_plan, hp.fwd_plan, hp.path[1]["plan"], hp.path[0]["plan"]]
+        bufs = [pl.exchange(x) for pl, x in zip(plans, local_in)]       # kept for the kernel-only timing
+    else:
+        full = [B.padded(hp.n, dims[0], dev, gen), B.padded(hp.n, dims[1], dev, gen),
+                torch.empty(hp.n, dims[1], device=dev), torch.empty(hp.n, dims[0], device=dev)]
+
+    compact_bwd = "plan" in hp.path[0]
+
+    def one(k):
+        if k >= 2 and compact_bwd:
+            hp.backward_halo(1 if k == 2 else 0, local_in[k], outs[k])
+        elif halo:
+            hp.forward_halo(local_in[k], outs[k])
+        else:
+            hp.gather(full[k], local_in[k])
+            (hp.forward(full[k], outs[k]) if k < 2 else hp.backward(1 if k == 2 else 0, full[k], outs[k]))
+
+    if compact_bwd and not halo:
+        bufs = [None, None, hp.path[1]["plan"].exchange(local_in[2]), hp.path[0]["plan"].exchange(local_in[3])]
+
+    def local_only(k):
+        if k < 2 and not halo:
+            return hp.forward(full[k], outs[k])
+        if k >= 2 and not compact_bwd:
+            return hp.backward(1 if k == 2 else 0, full[k], outs[k])
+        if k < 2:
+            return hp.capi.spmm_forward(bufs[k], hp.row, hp.col_c, hp.deg, hp.pp, hp.p2n, hp.part_size,
+                                        out=outs[k], deg_row=hp.deg_row, prescaled=True)
+        p = hp.path[1 if k == 2 else 0]
+        return hp.capi.spmm_backward_compacted(bufs[k], p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
+                                               hp.back_size, out=outs[k], deg_row=hp.deg_row, num_rows=n_loc)
 
     def step():
         for k in range(4):
-            hp.gather(full[k], local_in[k])
-            if k < 2:
-                hp.forward(full[k], outs[k])
-            else:
-                hp.backward(1 if k == 2 else 0, full[k], outs[k])
+            one(k)
 
     stream = torch.cuda.current_stream()
     for _ in range(max(args.warmup, 3)):
@@ -217,8 +459,8 @@ def run_bench(args, rank: int, world: int, dev):
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         k0.record(stream)
         for _ in range(args.steps):
-            hp.forward(full[0], outs[0]); hp.forward(full[1], outs[1])
-            hp.backward(1, full[2], outs[2]); hp.backward(0, full[3], outs[3])
+            for k in range(4):
+                local_only(k)
         k1.record(stream)
         torch.cuda.synchronize()
         kms = torch.tensor([k0.elapsed_time(k1) / args.steps], device=dev)
@@ -232,8 +474,7 @@ def run_bench(args, rank: int, world: int, dev):
     def e2e_step():
         for k in range(4):
             local_in[k].copy_(host_in[k], non_blocking=True)
-            hp.gather(full[k], local_in[k])
-            (hp.forward(full[k], outs[k]) if k < 2 else hp.backward(1 if k == 2 else 0, full[k], outs[k]))
+            one(k)
             host_out[k].copy_(outs[k], non_blocking=True)
 
     for _ in range(2):
@@ -266,9 +507,15 @@ def run_bench(args, rank: int, world: int, dev):
                                    f"backward part size {args.backsize}",
                        "seed": args.seed, "l2": "inputs exceed L2",
                        "parallelism": f"rows{world}: destination-row ranges with equal edge counts, "
-                                      f"one NCCL row all-gather per aggregation"},
+                                      + {"halo": "one NCCL all-to-all of the referenced source rows per aggregation",
+                                         "allgather": "contiguous ranges, one uneven NCCL row all-gather per aggregation",
+                                         "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
+                                                     "NCCL all-gather per aggregation"}[mode]},
             "local_spmm_ms": round(kms.item(), 4), "exchange_ms": round(ms.item() - kms.item(), 4),
-            "shards": {"edges": [int(t[0]) for t in gathered], "rows": [int(t[1]) for t in gathered]},
+            "shards": {"edges": [int(t[0]) for t in gathered], "rows": [int(t[1]) for t in gathered],
+                       "rank0_source_rows": ([pl.num_rows for pl in plans] if halo else
+                                             [hp.n, hp.n] + ([hp.path[1]["plan"].num_rows, hp.path[0]["plan"].num_rows]
+                                                             if compact_bwd else [hp.n, hp.n]))},
             "roofline": {"bound": "hbm", "kernel": "all four local SpMMs", "achieved": None, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": None, "traffic": None,
                          "note": "per-kernel roofline is reported by the 1-GPU run"},

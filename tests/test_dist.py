@@ -82,11 +82,29 @@ def _worker(rank, world, port, results):
             before = int((ref[i]["edge_mask"][:e0] != -1).sum())
             ok_prep &= np.array_equal(ids[:valid], ref[i]["id"][before:before + valid])
             ok_prep &= np.array_equal(cols[:valid], ref[i]["edgeList"][before:before + valid])
+        # --- halo exchange: only referenced rows travel, edges are re-indexed -----------------
+        plan = D.HaloPlan(torch.from_numpy(sh.indices), bounds, rank, world)
+        local_rows = torch.full((sh.num_rows, 24), -1.0)[:, :22]
+        local_rows.copy_(want[sh.v0:sh.v1])
+        buf = plan.exchange(local_rows)
+        ok_halo = bool(torch.equal(buf[plan.remap.long()], want[torch.from_numpy(sh.indices).long()]))
+        ok_halo &= plan.num_rows == len(np.unique(sh.indices)) and buf.stride(0) == 24
+        ok_halo &= bool(torch.equal(plan.needed, torch.from_numpy(np.unique(sh.indices)).long()))
+        # --- masked-row exchange over equal blocks (backward layers of the balanced mode) -----
+        n_eq = (n // world) * world
+        mask = torch.from_numpy(np.random.Generator(np.random.PCG64(3)).random(n_eq) < 0.2)
+        mg = D.MaskedGather(mask, n_eq // world, rank, world)
+        blk = n_eq // world
+        buf = mg.exchange(want[rank * blk:(rank + 1) * blk].clone())
+        sel = torch.nonzero(mask).view(-1)
+        ok_halo &= bool(torch.equal(buf[mg.pos[sel].long()], want[sel]))
+        ok_halo &= mg.num_rows == world * mg.cap and mg.cap == int(mask.view(world, blk).sum(1).max())
+        ok_halo &= bool(torch.equal(mg.compact(torch.arange(n_eq, dtype=torch.float32))[mg.pos[sel].long()], sel.float()))
         # --- d_weight partials add up -----------------------------------------------------
         part = torch.full((4, 3), float(rank + 1))
         dist.all_reduce(part)
         ok_sum = bool(torch.all(part == sum(range(1, world + 1))))
-        results[rank] = (ok_gather, bool(ok_prep), ok_sum)
+        results[rank] = (ok_gather, bool(ok_prep), ok_sum, bool(ok_halo))
     finally:
         dist.destroy_process_group()
 
@@ -97,4 +115,26 @@ def test_two_ranks_gloo():
     mgr = mp.get_context("spawn").Manager()
     results = mgr.dict()
     mp.spawn(_worker, args=(world, free_port(), results), nprocs=world, join=True)
-    assert dict(results) == {0: (True, True, True), 1: (True, True, True)}
+    assert dict(results) == {0: (True, True, True, True), 1: (True, True, True, True)}
+
+
+def test_balanced_relabel_gives_equal_rows_and_edges():
+    g = graphs.make_graph("pubmed", 0, cache=False)
+    n = g.num_nodes
+    for world in (1, 2, 3, 8):
+        new_of_old, n_loc = D.balanced_relabel(g.indptr, world)
+        assert n_loc == -(-n // world) and len(np.unique(new_of_old)) == n and new_of_old.max() < world * n_loc
+        old_of_new = np.full(world * n_loc, -1)
+        old_of_new[new_of_old] = np.arange(n)
+        edges = []
+        for r in range(world):
+            sh = D.make_relabelled_shard(g.indptr, g.indices, new_of_old, n_loc, r, world)
+            assert sh.num_rows == n_loc and sh.indptr[0] == 0 and sh.indptr[-1] == sh.num_edges
+            edges.append(sh.num_edges)
+            for lr in range(0, n_loc, max(1, n_loc // 50)):
+                old = old_of_new[r * n_loc + lr]
+                got = sh.indices[sh.indptr[lr]:sh.indptr[lr + 1]]
+                want = new_of_old[g.indices[g.indptr[old]:g.indptr[old + 1]]] if old >= 0 else np.zeros(0)
+                assert np.array_equal(got, want)
+        assert sum(edges) == g.num_edges
+        assert max(edges) - min(edges) <= np.diff(g.indptr).max()       # hubs are dealt out evenly

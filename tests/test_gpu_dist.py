@@ -1,0 +1,98 @@
+"""Row-partitioned aggregation on two real GPUs (NCCL) against the float64
+oracle of the whole graph, in all three partition/exchange modes.  Skipped on a
+machine with fewer than two GPUs."""
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, mode, results):
+    import os
+    os.environ["NCCL_NVLS_ENABLE"] = "0"          # plain peer transport is all this test needs
+    from eppgcn_b200 import dist as D
+    from eppgcn_b200 import graphs
+    from oracle import epp_oracle as O
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=dev)
+    try:
+        ds = graphs.load_workload("pubmed", 0)
+        g, n = ds.graph, ds.num_nodes
+        deg = ds.degrees.numpy().copy()
+        train = ds.train_mask.numpy().copy()
+        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange=mode)
+        sh = hp.shard
+        rng = np.random.Generator(np.random.PCG64(11))
+        mats = [rng.standard_normal((n, d)).astype(np.float32) for d in (16, 22)]
+        # this rank's rows of a whole-graph matrix, in the partition's own numbering
+        if hp.new_of_old is not None:
+            old_of_new = np.full(hp.n, -1, dtype=np.int64)
+            old_of_new[hp.new_of_old] = np.arange(n)
+            mine = old_of_new[sh.v0:sh.v1]
+        else:
+            mine = np.arange(sh.v0, sh.v1)
+        have = mine >= 0
+
+        def local_rows(m):
+            out = np.zeros((sh.num_rows, m.shape[1]), dtype=np.float32)
+            out[have] = m[mine[have]]
+            return torch.from_numpy(out).to(dev)
+
+        path, _ = O.prepare_execution_path(g.indptr, g.indices, train, 2, hp.part_size, [8, 8])
+        ok = True
+        for m in mats:
+            d = m.shape[1]
+            scaled = local_rows(m * deg[:, None])                       # rows as the update step leaves them
+            out = torch.empty(sh.num_rows, d, device=dev)
+            if mode == "halo":
+                hp.forward_halo(scaled, out)
+            else:
+                full = torch.empty(hp.n, d, device=dev)
+                hp.gather(full, scaled)
+                hp.forward(full, out)
+            want = O.spmm_forward(g.indptr, g.indices, deg, m)
+            err = np.abs(out.cpu().numpy()[have] - want[mine[have]]) - (2e-6 + 2e-5 * np.abs(want[mine[have]]))
+            ok &= bool(err.max() <= 0)
+            for i, conv in enumerate(path):
+                d_in = torch.empty(sh.num_rows, d, device=dev)
+                if "plan" in hp.path[i]:
+                    hp.backward_halo(i, local_rows(m), d_in)
+                else:
+                    full = torch.empty(hp.n, d, device=dev)
+                    hp.gather(full, local_rows(m))
+                    hp.backward(i, full, d_in)
+                wb = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, m,
+                                               conv["numParts"])
+                err = np.abs(d_in.cpu().numpy()[have] - wb[mine[have]]) - (2e-6 + 2e-5 * np.abs(wb[mine[have]]))
+                ok &= bool(err.max() <= 0)
+        # the sharded path sizes add up to the single-process ones
+        sizes = torch.tensor([p["valid"] for p in hp.path] + [p["parts"] for p in hp.path], device=dev)
+        dist.all_reduce(sizes)
+        ok &= sizes[:2].tolist() == [c["valid_len"] for c in path]
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo"])
+def test_two_gpus_match_the_whole_graph_oracle(mode):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(2, _free_port(), mode, results), nprocs=2, join=True)
+    assert dict(results) == {0: True, 1: True}

@@ -27,6 +27,7 @@ SIGNATURES = {
     "eppgcn_spmm_forward": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_spmm_backward_compacted": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P]),
+    "eppgcn_probe_gather": (_I, [_P, _LL, _P, _LL, _I, _P, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
@@ -146,6 +147,15 @@ def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts,
         _dev(deg_row, torch.float32, "deg_row"), _dev(degrees, torch.float32, "degrees"),
         n, dim, int(num_parts), part_size, blockx, blocky, _stream()))
     return out
+
+
+def probe_gather(col_idx, feat, sink=None):
+    """Enqueues the bare gather of ``feat`` rows over ``col_idx`` (a measurement aid)."""
+    if sink is None:
+        sink = torch.zeros(1, device=feat.device)
+    check(lib().eppgcn_probe_gather(_dev(col_idx, torch.int32, "col_idx"), col_idx.numel(), feat.data_ptr(),
+                                    _row_stride(feat, "feat"), feat.size(1), sink.data_ptr(), _stream()))
+    return sink
 
 
 def mask_forward(ids, part_ptr, edge_list, src_mask, ngh_mask, back_edge_mask, node_degs,

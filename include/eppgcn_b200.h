@@ -207,6 +207,18 @@ int eppgcn_split_parts(const int *node_deg, int num_nodes, int part_size,
 int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Measurement aid, no counterpart in the reference: performs only the gather
+ * of an aggregation -- for every entry of col_idx the fp32 row
+ * feat[col_idx[e]][0..dim) is loaded (16-byte loads) and discarded.  No
+ * weights, no result.  Its duration is the floor for any aggregation over the
+ * same column stream and row width on the device at hand; bench.py reports it
+ * beside the kernels' times.  dim <= 128; rows 16-byte aligned (feat_ld a
+ * multiple of 4 floats, >= dim rounded up to 4).  sink: one device float.
+ */
+int eppgcn_probe_gather(const int *col_idx, long long num_edges, const float *feat, long long feat_ld,
+                        int dim, float *sink, void *stream);
+
+/* ------------------------------------------------------------------------
  * Host-side helpers (CPU pointers, synchronous).
  */
 /* Neighbour-group partition, replaces build_part

@@ -204,7 +204,9 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    if world > 1:
+    spec0 = graphs.WORKLOADS[args.workload]
+    if world > 1 or spec0.get("draw") == "device":
+        # several ranks, or a workload that is drawn on the GPU: the row-partitioned driver (also at one rank)
         from eppgcn_b200 import dist as epp_dist
         return epp_dist.run_bench(args, rank, world, dev)
 

@@ -105,6 +105,29 @@ def make_relabelled_shard(indptr: np.ndarray, indices: np.ndarray, new_of_old: n
     return RowShard(rank, rank * n_loc, (rank + 1) * n_loc, local.astype(np.int32), cols)
 
 
+def balanced_shard_device(indptr: torch.Tensor, indices: torch.Tensor, rank: int, world: int):
+    """Torch twin of :func:`balanced_relabel` + :func:`make_relabelled_shard`
+    for graphs that already live on a device.  Returns ``(new_of_old int64[N],
+    n_loc, local_indptr int32[n_loc+1], cols int32[local edges])``."""
+    dev = indptr.device
+    deg = (indptr[1:] - indptr[:-1]).long()
+    n = deg.numel()
+    n_loc = -(-n // world)
+    order = torch.sort(deg, descending=True, stable=True).indices
+    i = torch.arange(n, device=dev)
+    new_of_old = torch.empty(n, dtype=torch.int64, device=dev)
+    new_of_old[order] = (i % world) * n_loc + i // world
+    mine = order[rank::world]                       # old ids of this rank's rows, in local row order
+    lens = torch.zeros(n_loc, dtype=torch.int64, device=dev)
+    lens[:mine.numel()] = deg[mine]
+    local = torch.zeros(n_loc + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(lens, 0, out=local[1:])
+    first = indptr[mine].long() - local[:mine.numel()]
+    src = torch.repeat_interleave(first, lens[:mine.numel()]) + torch.arange(int(local[-1]), device=dev)
+    cols = new_of_old[indices[src].long()].to(torch.int32)
+    return new_of_old, n_loc, local.to(torch.int32), cols
+
+
 def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None):
     """Fills ``full[b[r]:b[r+1]]`` on every rank with rank ``r``'s ``local``
     rows.  Row counts differ between ranks, so the exchange is one broadcast
@@ -273,9 +296,26 @@ class DistHotPath:
         self.capi, self.dev, self.rank, self.world, self.group = capi, dev, rank, world, group
         self.mode = exchange
         gnna = eppgcn_b200.load_gnnadvisor()
-        g = ds.graph
-        degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
-        if exchange == "balanced":
+        on_device = torch.is_tensor(getattr(ds, "indptr", None))      # DeviceWorkload: the graph never touches the host
+        if on_device:
+            if exchange != "balanced":
+                raise ValueError("device-resident workloads support the balanced mode only")
+            new_of_old, n_loc, local_ptr, cols = balanced_shard_device(ds.indptr, ds.indices, rank, world)
+            self.new_of_old = new_of_old
+            self.n = n_loc * world
+            self.bounds = np.arange(world + 1, dtype=np.int64) * n_loc
+            sh = RowShard(rank, rank * n_loc, (rank + 1) * n_loc, local_ptr.cpu(), cols)
+            deg_t = torch.ones(self.n, device=dev)
+            deg_t[new_of_old] = ds.degrees.to(dev)
+            train_t = torch.zeros(self.n, dtype=torch.bool, device=dev)
+            train_t[new_of_old] = ds.train_mask.to(dev)
+            del new_of_old
+        else:
+            g = ds.graph
+            degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
+        if on_device:
+            pass
+        elif exchange == "balanced":
             # relabelled graph: equal rows per rank, hubs dealt out; every per-vertex array follows the new ids
             self.new_of_old, n_loc = balanced_relabel(g.indptr, world)
             self.n = n_loc * world
@@ -294,14 +334,15 @@ class DistHotPath:
         self.shard = sh
         self.part_size = max(int(ds.avg_degree), 1)
         L = ds.num_layers
-        row_cpu = torch.from_numpy(sh.indptr)
+        row_cpu = sh.indptr if on_device else torch.from_numpy(sh.indptr)
         pp, p2n = gnna.build_part(self.part_size, row_cpu)
-        self.row, self.col = row_cpu.to(dev), torch.from_numpy(sh.indices).to(dev)
+        self.row = row_cpu.to(dev)
+        self.col = sh.indices if on_device else torch.from_numpy(sh.indices).to(dev)
         self.pp, self.p2n = pp.to(dev), p2n.to(dev)
-        self.deg = torch.from_numpy(degrees_np).to(dev)
+        self.deg = deg_t if on_device else torch.from_numpy(degrees_np).to(dev)
         self.deg_row = self.deg[sh.v0:sh.v1]
         n_loc, e_loc = sh.num_rows, sh.num_edges
-        train = torch.from_numpy(train_np).to(dev)
+        train = train_t if on_device else torch.from_numpy(train_np).to(dev)
         ngh = [torch.zeros(self.n, dtype=torch.bool, device=dev) for _ in range(L - 1)]
         edge_masks = [torch.full((e_loc,), -1, dtype=torch.int32, device=dev) for _ in range(L)]
         node_degs = [torch.zeros(n_loc, dtype=torch.int32, device=dev) for _ in range(L)]
@@ -377,74 +418,91 @@ class DistHotPath:
 
 
 def run_bench(args, rank: int, world: int, dev):
-    """Multi-GPU arm of bench.py: the same four aggregations, row-partitioned,
-    each preceded by the all-gather of its source rows.  Strong scaling: the
-    graph is fixed and split over the ranks."""
+    """Multi-GPU arm of bench.py: the forward and backward aggregations of every
+    layer, row-partitioned, each preceded by the exchange of its source rows.
+    Strong scaling: the graph is fixed and split over the ranks.  Workloads whose
+    ``WORKLOADS`` entry is too large for the host generator are drawn on the GPU
+    (every rank draws the same graph from the same seed)."""
     from eppgcn_b200 import graphs
     import bench as B
-    dist.init_process_group("nccl", device_id=dev)
+    if not dist.is_initialized():
+        if "MASTER_ADDR" in os.environ:
+            dist.init_process_group("nccl", device_id=dev)
+        else:       # plain `python bench.py` with a device-drawn workload: a group of one
+            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1,
+                                    device_id=dev)
     spec = graphs.WORKLOADS[args.workload]
-    if rank == 0:
-        ds = graphs.load_workload(args.workload, args.seed)      # generates and caches the graph once per box
-    dist.barrier()
-    if rank != 0:
-        ds = graphs.load_workload(args.workload, args.seed)
-    n, e = ds.num_nodes, ds.num_edges
-    dims = [spec["hidden"], spec["classes"]]
-    mode = getattr(args, "exchange", "balanced")
+    device_drawn = spec.get("draw") == "device"
+    t0 = time.perf_counter()
+    if device_drawn:
+        ds = graphs.DeviceWorkload(args.workload, args.seed, dev)
+    else:
+        if rank == 0:
+            ds = graphs.load_workload(args.workload, args.seed)      # generates and caches the graph once per box
+        dist.barrier()
+        if rank != 0:
+            ds = graphs.load_workload(args.workload, args.seed)
+    n, e, L = ds.num_nodes, ds.num_edges, ds.num_layers
+    dims = [spec["hidden"]] * (L - 1) + [spec["classes"]]
+    mode = "balanced" if device_drawn else getattr(args, "exchange", "balanced")
     halo = mode == "halo"
     hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode)
+    if device_drawn:
+        ds.indptr = ds.indices = None           # the shard is all this rank needs from here on
+        torch.cuda.empty_cache()
+    setup_s = time.perf_counter() - t0
     n_loc = hp.shard.num_rows
     gen = torch.Generator(device=dev).manual_seed(args.seed + rank)
-    widths = (dims[0], dims[1], dims[1], dims[0])
+    # operations of one epoch: forward of every layer, then backward from the last layer down
+    ops = [("fwd", i, dims[i]) for i in range(L)] + [("bwd", i, dims[i]) for i in reversed(range(L))]
     # forward inputs as the update step leaves them (padded rows), backward inputs as autograd does (dense)
-    local_in = [B.padded(n_loc, dims[0], dev, gen), B.padded(n_loc, dims[1], dev, gen),
-                torch.randn(n_loc, dims[1], device=dev, generator=gen),
-                torch.randn(n_loc, dims[0], device=dev, generator=gen)]
-    outs = [torch.empty(n_loc, d, device=dev) for d in widths]
-    if halo:
-        plans = [hp.fwd_plan, hp.fwd_plan, hp.path[1]["plan"], hp.path[0]["plan"]]
-        bufs = [pl.exchange(x) for pl, x in zip(plans, local_in)]       # kept for the kernel-only timing
-    else:
-        full = [B.padded(hp.n, dims[0], dev, gen), B.padded(hp.n, dims[1], dev, gen),
-                torch.empty(hp.n, dims[1], device=dev), torch.empty(hp.n, dims[0], device=dev)]
-
+    local_in = [B.padded(n_loc, d, dev, gen) if kind == "fwd" else torch.randn(n_loc, d, device=dev, generator=gen)
+                for kind, _, d in ops]
+    outs = [torch.empty(n_loc, d, device=dev) for _, _, d in ops]
     compact_bwd = "plan" in hp.path[0]
+    full = [None] * len(ops)
+    bufs = [None] * len(ops)
+    for k, (kind, i, d) in enumerate(ops):
+        if halo:
+            bufs[k] = (hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).exchange(local_in[k])
+        elif kind == "bwd" and compact_bwd:
+            bufs[k] = hp.path[i]["plan"].exchange(local_in[k])
+        else:
+            full[k] = B.padded(hp.n, d, dev, gen) if kind == "fwd" else torch.empty(hp.n, d, device=dev)
 
     def one(k):
-        if k >= 2 and compact_bwd:
-            hp.backward_halo(1 if k == 2 else 0, local_in[k], outs[k])
+        kind, i, _ = ops[k]
+        if kind == "bwd" and compact_bwd:
+            hp.backward_halo(i, local_in[k], outs[k])
         elif halo:
             hp.forward_halo(local_in[k], outs[k])
         else:
             hp.gather(full[k], local_in[k])
-            (hp.forward(full[k], outs[k]) if k < 2 else hp.backward(1 if k == 2 else 0, full[k], outs[k]))
-
-    if compact_bwd and not halo:
-        bufs = [None, None, hp.path[1]["plan"].exchange(local_in[2]), hp.path[0]["plan"].exchange(local_in[3])]
+            (hp.forward(full[k], outs[k]) if kind == "fwd" else hp.backward(i, full[k], outs[k]))
 
     def local_only(k):
-        if k < 2 and not halo:
-            return hp.forward(full[k], outs[k])
-        if k >= 2 and not compact_bwd:
-            return hp.backward(1 if k == 2 else 0, full[k], outs[k])
-        if k < 2:
+        kind, i, _ = ops[k]
+        if kind == "fwd":
+            if not halo:
+                return hp.forward(full[k], outs[k])
             return hp.capi.spmm_forward(bufs[k], hp.row, hp.col_c, hp.deg, hp.pp, hp.p2n, hp.part_size,
                                         out=outs[k], deg_row=hp.deg_row, prescaled=True)
-        p = hp.path[1 if k == 2 else 0]
+        if not compact_bwd:
+            return hp.backward(i, full[k], outs[k])
+        p = hp.path[i]
         return hp.capi.spmm_backward_compacted(bufs[k], p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
                                                hp.back_size, out=outs[k], deg_row=hp.deg_row, num_rows=n_loc)
 
     def step():
-        for k in range(4):
+        for k in range(len(ops)):
             one(k)
 
     stream = torch.cuda.current_stream()
-    for _ in range(max(args.warmup, 3)):
-        step()
-    torch.cuda.synchronize()
-    dist.barrier()
     with B.ClockSampler(dev.index) as clocks:
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         dist.barrier()
@@ -459,7 +517,7 @@ def run_bench(args, rank: int, world: int, dev):
         k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         k0.record(stream)
         for _ in range(args.steps):
-            for k in range(4):
+            for k in range(len(ops)):
                 local_only(k)
         k1.record(stream)
         torch.cuda.synchronize()
@@ -472,7 +530,7 @@ def run_bench(args, rank: int, world: int, dev):
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
 
     def e2e_step():
-        for k in range(4):
+        for k in range(len(ops)):
             local_in[k].copy_(host_in[k], non_blocking=True)
             one(k)
             host_out[k].copy_(outs[k], non_blocking=True)
@@ -497,33 +555,36 @@ def run_bench(args, rank: int, world: int, dev):
     dist.all_gather(gathered, edges)
     if rank == 0:
         peak, peak_src = B.measured_peak_gbs()
-        algo = B.bytes_forward(n, e, dims[0]) + B.bytes_forward(n, e, dims[1])
+        exchanged = [(bufs[k].size(0) if bufs[k] is not None else hp.n) for k in range(len(ops))]
         line = {
-            "metric": "2-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms.item(), 4), "unit": "ms/epoch",
-            "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms.item(), 4),
-            "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: N={n}, E={e} directed incl. self loops, dims {dims[0]}/{dims[1]}, "
-                                   f"train_ratio {spec['train_ratio']}, group size {hp.part_size}, "
-                                   f"backward part size {args.backsize}",
+            "metric": f"{L}-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms.item(), 4),
+            "unit": "ms/epoch", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": round(ms.item(), 4), "higher_is_better": False, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: N={n}, E={e} directed incl. self loops, dims "
+                                   f"{'/'.join(str(d) for d in dims)}, train_ratio {spec['train_ratio']}, "
+                                   f"group size {hp.part_size}, backward part size {args.backsize}"
+                                   + (", graph drawn on the GPU" if device_drawn else ""),
                        "seed": args.seed, "l2": "inputs exceed L2",
-                       "parallelism": f"rows{world}: destination-row ranges with equal edge counts, "
-                                      + {"halo": "one NCCL all-to-all of the referenced source rows per aggregation",
+                       "parallelism": f"rows{world}: "
+                                      + {"halo": "contiguous ranges, one NCCL all-to-all of the referenced source "
+                                                 "rows per aggregation",
                                          "allgather": "contiguous ranges, one uneven NCCL row all-gather per aggregation",
                                          "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
-                                                     "NCCL all-gather per aggregation"}[mode]},
+                                                     "NCCL all-gather per aggregation (source-mask rows only for "
+                                                     "the backward layers)"}[mode]},
             "local_spmm_ms": round(kms.item(), 4), "exchange_ms": round(ms.item() - kms.item(), 4),
             "shards": {"edges": [int(t[0]) for t in gathered], "rows": [int(t[1]) for t in gathered],
-                       "rank0_source_rows": ([pl.num_rows for pl in plans] if halo else
-                                             [hp.n, hp.n] + ([hp.path[1]["plan"].num_rows, hp.path[0]["plan"].num_rows]
-                                                             if compact_bwd else [hp.n, hp.n]))},
-            "roofline": {"bound": "hbm", "kernel": "all four local SpMMs", "achieved": None, "peak": peak,
+                       "source_rows_per_aggregation": exchanged},
+            "roofline": {"bound": "hbm", "kernel": "all local SpMMs", "achieved": None, "peak": peak,
                          "peak_source": peak_src, "unit": "GB/s", "frac": None, "traffic": None,
-                         "note": "per-kernel roofline is reported by the 1-GPU run"},
+                         "note": "per-kernel roofline is reported by the 1-GPU run of the default workload"},
             "clocks": clocks.summary(),
             "e2e": {"value": round(e2e.item(), 4), "unit": "ms/epoch", "h2d_bytes_per_step": int(byts[0]),
                     "d2h_bytes_per_step": int(byts[1]),
                     "what": "each rank stages its rows from pinned host memory, exchanges, aggregates, copies results back"},
-            "gpu_launches": 4 * args.steps, "cpu_baseline": None,
+            "gpu_launches": len(ops) * args.steps, "cpu_baseline": None,
+            "setup_s": round(setup_s, 2), "prep_s": round(hp.prep_s, 4),
         }
         print(json.dumps(line), flush=True)
     dist.barrier()

@@ -166,8 +166,11 @@ WORKLOADS = {
                    dim=96, hidden=16, classes=22, layers=2, train_ratio=0.1, x="uniform"),
     "rmat21": dict(kind="rmat", scale=21, edge_factor=8, a=0.57, b=0.19, c=0.19,
                    dim=128, hidden=16, classes=22, layers=2, train_ratio=0.1, x="normal"),
-    "rmat24": dict(kind="rmat", scale=24, edge_factor=16, a=0.57, b=0.19, c=0.19,
+    "rmat24": dict(kind="rmat", scale=24, edge_factor=16, a=0.57, b=0.19, c=0.19, draw="device",
                    dim=128, hidden=64, classes=32, layers=3, train_ratio=0.05, x="normal"),
+    # the same 3-layer shape at a size that draws in a second (tests of the device-drawn path)
+    "rmat18x3": dict(kind="rmat", scale=18, edge_factor=16, a=0.57, b=0.19, c=0.19, draw="device",
+                     dim=128, hidden=64, classes=32, layers=3, train_ratio=0.05, x="normal"),
     # small R-MAT used by tests and profiler captures (same generator, fewer levels)
     "rmat16": dict(kind="rmat", scale=16, edge_factor=8, a=0.57, b=0.19, c=0.19,
                    dim=128, hidden=16, classes=22, layers=2, train_ratio=0.1, x="normal"),
@@ -278,3 +281,75 @@ def load_workload(name: str, seed: int = 0, device="cpu", train_ratio: float | N
     ds.hidden = spec["hidden"]
     ds.name = name
     return ds
+
+
+# ---------------------------------------------------------------------------
+# Device-side generation for the workloads that are too large to draw on the
+# host in reasonable time (R-MAT scale 24: 268 M pairs, 24 levels each).
+# ---------------------------------------------------------------------------
+def rmat_csr_device(scale: int, pairs_per_vertex: int, a: float, b: float, c: float, seed: int, device):
+    """R-MAT CSR built on ``device``: ``pairs_per_vertex * 2**scale`` draws,
+    mirrored, de-duplicated, self edges replaced by one self loop per vertex.
+    Unlike the host generator the duplicate draws are not replaced, so the edge
+    count is a little below the nominal one (as in Graph500).  The same seed on
+    the same GPU model gives the same graph, so every rank can draw its own copy.
+    Returns ``(indptr int32[N+1], indices int32[E])`` on the device."""
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    n = 1 << scale
+    total = pairs_per_vertex * n
+    ab, abc = a + b, a + b + c
+    keys = []
+    chunk = 1 << 26
+    for start in range(0, total, chunk):
+        m = min(chunk, total - start)
+        src = torch.zeros(m, dtype=torch.int64, device=dev)
+        dst = torch.zeros(m, dtype=torch.int64, device=dev)
+        for _ in range(scale):
+            r = torch.rand(m, device=dev, generator=gen)
+            src = (src << 1) | (r >= ab)
+            dst = (dst << 1) | (((r >= a) & (r < ab)) | (r >= abc))
+        keep = src != dst
+        src, dst = src[keep], dst[keep]
+        keys.append(src * n + dst)
+        keys.append(dst * n + src)
+        del src, dst, keep, r
+    loops = torch.arange(n, dtype=torch.int64, device=dev)
+    keys.append(loops * n + loops)
+    key = torch.cat(keys)
+    del keys, loops
+    key = torch.unique(key)                       # sorted, distinct (row-major order)
+    if key.numel() >= 2 ** 31:
+        raise ValueError("edge count exceeds int32 indexing")
+    rows = key >> scale
+    indices = (key & (n - 1)).to(torch.int32)
+    del key
+    counts = torch.bincount(rows, minlength=n)
+    del rows
+    indptr = torch.zeros(n + 1, dtype=torch.int64, device=dev)
+    torch.cumsum(counts, 0, out=indptr[1:])
+    return indptr.to(torch.int32), indices
+
+
+class DeviceWorkload:
+    """A workload whose graph lives on the GPU from the start: the fields the
+    hot path needs, named as in :class:`SyntheticDataset`."""
+
+    def __init__(self, name: str, seed: int, device, train_ratio: float | None = None):
+        spec = WORKLOADS[name]
+        if spec["kind"] != "rmat":
+            raise ValueError("device-side generation is implemented for the R-MAT workloads")
+        dev = torch.device(device)
+        self.name, self.seed, self.device = name, seed, dev
+        self.indptr, self.indices = rmat_csr_device(spec["scale"], spec["edge_factor"], spec["a"], spec["b"],
+                                                    spec["c"], seed, dev)
+        self.num_nodes = self.indptr.numel() - 1
+        self.num_edges = self.indices.numel()
+        self.avg_degree = self.num_edges / self.num_nodes
+        self.num_features, self.num_classes = spec["dim"], spec["classes"]
+        self.num_layers, self.hidden = spec["layers"], spec["hidden"]
+        deg = (self.indptr[1:] - self.indptr[:-1]).clamp(min=1).float()
+        self.degrees = deg.rsqrt()
+        gen = torch.Generator(device=dev).manual_seed(seed + 2)
+        ratio = spec["train_ratio"] if train_ratio is None else train_ratio
+        self.train_mask = torch.rand(self.num_nodes, device=dev, generator=gen) < ratio

@@ -39,8 +39,8 @@ sys.path.insert(0, ROOT)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of each aggregation kernel on the default
 # workload (rmat21, seed 0), from the ncu capture summarised in profiles/staged_spmm_rmat21_ncu_full.md.
-NCU_DRAM_TRAFFIC = {"fwd_d16": 630_500_000, "fwd_d22": 971_800_000,
-                    "bwd_conv2_d22": 135_800_000, "bwd_conv1_d16": 493_100_000}
+NCU_DRAM_TRAFFIC = {"fwd_d16": 590_400_000, "fwd_d22": 903_200_000,
+                    "bwd_conv2_d22": 136_700_000, "bwd_conv1_d16": 492_700_000}
 
 
 def log(*a):

@@ -26,7 +26,8 @@ SIGNATURES = {
     "eppgcn_last_error": (C.c_char_p, []),
     "eppgcn_spmm_forward": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_spmm_backward_compacted": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
-    "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _I, _I, _P]),
+    "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
+    "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
     "eppgcn_probe_gather": (_I, [_P, _LL, _P, _LL, _I, _P, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
@@ -107,9 +108,18 @@ def update_scaled(x, w, scale=None, pad_to=8):
     ld = (dout + pad_to - 1) // pad_to * pad_to
     full = torch.empty(n, ld, device=x.device, dtype=torch.float32)
     check(lib().eppgcn_update_scaled(
-        full.data_ptr(), ld, x.data_ptr(), _row_stride(x, "x"), _dev(w, torch.float32, "w"),
-        None if scale is None else _dev(scale, torch.float32, "scale"), n, k, dout, _stream()))
+        full.data_ptr(), ld, x.data_ptr(), _row_stride(x, "x"), _dev(w, torch.float32, "w"), dout,
+        None if scale is None else _dev(scale, torch.float32, "scale"), n, k, dout, ld - dout, _stream()))
     return full[:, :dout]
+
+
+def weight_grad(x, d):
+    """``x.T @ d`` for a tall ``x [N, k]`` and ``d [N, dout]``."""
+    k, dout = x.size(1), d.size(1)
+    dw = torch.empty(k, dout, device=x.device, dtype=torch.float32)
+    check(lib().eppgcn_weight_grad(dw.data_ptr(), x.data_ptr(), _row_stride(x, "x"), d.data_ptr(),
+                                   _row_stride(d, "d"), x.size(0), k, dout, _stream()))
+    return dw
 
 
 def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size=0, dim_worker=32,

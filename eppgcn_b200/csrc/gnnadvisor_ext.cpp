@@ -60,14 +60,43 @@ torch::Tensor update_scaled_padded(const torch::Tensor &x, const torch::Tensor &
   const bool aligned = x.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr<float>()) % 16 == 0;
   if (d <= 32 && aligned && n > 0) {
     epp_check(eppgcn_update_scaled(full.data_ptr<float>(), ld, x.data_ptr<float>(), x.stride(0), w.data_ptr<float>(),
-                                   degrees.data_ptr<float>(), static_cast<int>(n), static_cast<int>(k),
-                                   static_cast<int>(d), current_stream()),
+                                   d, degrees.data_ptr<float>(), static_cast<int>(n), static_cast<int>(k),
+                                   static_cast<int>(d), static_cast<int>(ld - d), current_stream()),
               "eppgcn_update_scaled");
   } else {
     at::mm_out(view, x, w);
     view.mul_(degrees.narrow(0, 0, n).unsqueeze(1));
   }
   return view;
+}
+
+// The two dense products of a layer's backward (EPPGCN_kernel.cu:614-615):
+//   d_input = d' @ W^T   [N, Din]      d_weight = X^T @ d'   [Din, Dout]
+// Both are tall and skinny; the library's FP32 FMA kernels read X and write
+// d_input once, where cuBLAS takes several times longer on these shapes.  Shapes
+// outside the kernels' limits go through torch::mm.
+std::vector<torch::Tensor> backward_update(const torch::Tensor &d_prime, const torch::Tensor &X,
+                                           const torch::Tensor &W) {
+  const int64_t n = d_prime.size(0), dout = d_prime.size(1), din = W.size(0);
+  const bool ok = n > 0 && n < (1LL << 31) && dout <= 32 && din * ((dout + 3) / 4 * 4) <= 4096 && din % 4 == 0 &&
+                  X.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(X.data_ptr<float>()) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(d_prime.data_ptr<float>()) % 16 == 0;
+  if (!ok) return {at::mm(d_prime, W.transpose(0, 1)), at::mm(X.transpose(0, 1), d_prime)};
+  auto wt = W.transpose(0, 1).contiguous();                 // [Dout, Din]
+  auto d_input = at::empty({n, din}, d_prime.options());
+  for (int64_t c0 = 0; c0 < din; c0 += 32) {                // 32 output columns per launch
+    const int cols = static_cast<int>(std::min<int64_t>(32, din - c0));
+    epp_check(eppgcn_update_scaled(d_input.data_ptr<float>() + c0, din, d_prime.data_ptr<float>(), dout,
+                                   wt.data_ptr<float>() + c0, din, nullptr, static_cast<int>(n),
+                                   static_cast<int>(dout), cols, 0, current_stream()),
+              "eppgcn_update_scaled");
+  }
+  auto d_weight = at::empty({din, dout}, d_prime.options());
+  epp_check(eppgcn_weight_grad(d_weight.data_ptr<float>(), X.data_ptr<float>(), X.stride(0),
+                               d_prime.data_ptr<float>(), dout, static_cast<int>(n), static_cast<int>(din),
+                               static_cast<int>(dout), current_stream()),
+            "eppgcn_weight_grad");
+  return {d_input, d_weight};
 }
 
 torch::Tensor aggregate_forward(const torch::Tensor &feat, const torch::Tensor &row_pointers,
@@ -133,9 +162,7 @@ std::vector<torch::Tensor> spmm_backward(torch::Tensor d_output, torch::Tensor X
                                       partSize, dimWorker, warpPerBlock);
   }
   ScopedTime t(3);
-  auto d_input = at::mm(d_input_prime, W.transpose(0, 1));
-  auto d_weight = at::mm(X.transpose(0, 1), d_input_prime);
-  return {d_input, d_weight};
+  return backward_update(d_input_prime, X, W);
 }
 
 // mask_forward(id, partPointer, edgeList, src_mask, ngh_mask, backEdgeMask,
@@ -191,9 +218,7 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
               "eppgcn_spmm_backward_compacted");
   }
   ScopedTime t(3);
-  auto d_input = at::mm(d_input_prime, W.transpose(0, 1));
-  auto d_weight = at::mm(X.transpose(0, 1), d_input_prime);
-  return {d_input, d_weight};
+  return backward_update(d_input_prime, X, W);
 }
 
 // build_part(partSize, indptr) -> [partPtr, part2Node]      EPPGCN.cpp:186-227

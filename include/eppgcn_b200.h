@@ -102,15 +102,35 @@ int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_
  *   out[r][c] = scale[r] * sum_k x[r][k] * w[k][c]        c < dout <= 32
  *
  * FP32 FMA on the CUDA cores (no reduced-precision tensor-core path).
- * x    [num_rows] rows of stride ldx floats, w [k][dout] dense row-major,
- * out  rows of stride ld_out floats (ld_out >= dout); columns dout..ld_out-1
- *      of a padded row are written with zeros when ld_out covers them.
- * scale may be NULL (plain x @ w).  x and out rows must be 16-byte aligned
- * (strides multiples of 4 floats).  dout > 32 returns EPP_ERR_TOO_LARGE.
+ * x    [num_rows] rows of stride ldx floats, w [k] rows of stride ldw floats,
+ * out  rows of stride ld_out floats; the call writes columns 0..dout-1 and
+ *      zero-fills the pad_cols columns after them (ld_out >= dout + pad_cols).
+ *      A 32-column block of a wider result is written by offsetting `out`
+ *      and `w` and passing pad_cols = 0.
+ * scale may be NULL (plain x @ w).  out rows must be 16-byte aligned (ld_out a
+ * multiple of 4 floats); x is read fastest when ldx is a multiple of 4 too.
+ * dout > 32 returns EPP_ERR_TOO_LARGE (call once per 32-column block).
+ * Also used for d_input = d' @ W^T of the backward wrapper
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:614) with w = W^T.
  */
 int eppgcn_update_scaled(float *out, long long ld_out, const float *x, long long ldx,
-                         const float *w, const float *scale,
-                         int num_rows, int k, int dout, void *stream);
+                         const float *w, long long ldw, const float *scale,
+                         int num_rows, int k, int dout, int pad_cols, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Weight gradient of a layer, replaces torch::mm(X.transpose(0,1), d_input_prime)
+ * of the backward wrapper (EPPGCN/GCNConv/EPPGCN_kernel.cu:615).
+ *
+ *   dw[kk][c] = sum_r x[r][kk] * d[r][c]        dw dense [k][dout], overwritten
+ *
+ * FP32 FMA; partial sums of row slabs are combined with atomics, so the
+ * summation order varies from run to run.  dout <= 32 and k * dout <= 4096
+ * (after rounding both up to multiples of 4), else EPP_ERR_TOO_LARGE.
+ * x and d must be 16-byte aligned; strides that are multiples of 4 floats are
+ * read with 16-byte copies.
+ */
+int eppgcn_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd,
+                       int num_rows, int k, int dout, void *stream);
 
 /* ------------------------------------------------------------------------
  * Execution-path marking for one preparation step.

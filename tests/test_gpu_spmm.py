@@ -173,3 +173,49 @@ def test_forward_prescaled_rows(cuda, dim):
     got = capi.spmm_forward(scaled, t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda), t(p2n, cuda), 6,
                             prescaled=True)
     assert_close(got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), 2e-5, 2e-6, f"prescaled dim {dim}")
+
+
+@pytest.mark.parametrize("n,k,dout", [(1, 4, 4), (31, 16, 22), (32, 16, 22), (1000, 128, 16), (5000, 7, 5),
+                                      (100_003, 128, 16), (4097, 128, 32), (70_000, 16, 22)])
+def test_weight_grad(cuda, n, k, dout):
+    """X^T d' with FP32 FMA and atomically combined slabs, against float64."""
+    rng = np.random.Generator(np.random.PCG64(n + k))
+    x = rng.standard_normal((n, k)).astype(np.float32)
+    d = rng.standard_normal((n, dout)).astype(np.float32)
+    d[rng.random(n) < 0.5] = 0.0                                   # rows off the execution path
+    got = capi.weight_grad(t(x, cuda), t(d, cuda)).cpu().numpy()
+    want = x.astype(np.float64).T @ d.astype(np.float64)
+    mag = np.abs(x.astype(np.float64)).T @ np.abs(d.astype(np.float64))
+    assert got.shape == (k, dout)
+    assert np.all(np.abs(got - want) <= 1e-6 + 1e-6 * mag * max(1.0, np.sqrt(n) / 8)), \
+        f"worst {np.abs(got - want).max():.3e}"
+
+
+def test_weight_grad_limits(cuda):
+    with pytest.raises(capi.EppError) as e:
+        capi.weight_grad(torch.zeros(8, 512, device=cuda), torch.zeros(8, 32, device=cuda))
+    assert e.value.status == capi.EPP_ERR_TOO_LARGE
+
+
+def test_operator_backward_products_match_float64(cuda):
+    """ours_backward's d_input and d_weight through the FMA kernels (Din 128 -> four 32-column launches)."""
+    import eppgcn_b200
+    gnna = eppgcn_b200.load_gnnadvisor()
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(3))
+    for din, dout in ((128, 16), (16, 22)):
+        x = rng.standard_normal((n, din)).astype(np.float32)
+        w = rng.uniform(-0.3, 0.3, (din, dout)).astype(np.float32)
+        d_out = rng.standard_normal((n, dout)).astype(np.float32)
+        conv = make_path(indptr, indices, 0.2, 1, 6, 8, seed=din)[0]
+        d_in, d_w = gnna.ours_backward(t(d_out, cuda), t(x, cuda), t(w, cuda), t(conv["id"], cuda),
+                                       t(conv["partPointer"], cuda), t(conv["edgeList"], cuda), t(deg, cuda),
+                                       8, conv["numParts"], 1, 4, 16)
+        wi, ww, _ = O.gcn_layer_backward(d_out, x, w, conv["id"], conv["partPointer"], conv["edgeList"], deg,
+                                         conv["numParts"])
+        assert d_in.shape == (n, din) and d_w.shape == (din, dout)
+        assert_close(d_in.cpu().numpy(), wi, 2e-5, 2e-6, f"d_input {din}->{dout}")
+        s = float(np.abs(ww).max())
+        assert_close(d_w.cpu().numpy() / s, ww / s, 1e-4, 1e-5, f"d_weight {din}->{dout}")

@@ -270,6 +270,10 @@ __global__ void zero_tail_kernel(int *a, int *b, const int *count_dev, int skip,
 
 __global__ void publish_status_kernel(const ScanHeader *hdr, int *status_dev) { *status_dev = hdr->error; }
 
+// Self-test of the bounded wait: makes the first ticket 1, so tile 0 -- whose
+// descriptor the look-back of tile 1 needs -- never exists.
+__global__ void skip_first_ticket_kernel(ScanHeader *hdr) { hdr->ticket = 1u; }
+
 // ---------------------------------------------------------------------------
 // splitting active rows into parts
 // ---------------------------------------------------------------------------
@@ -411,7 +415,8 @@ EPP_EXPORT int eppgcn_compact_mask(const int *edge_mask, const int *col_idx, int
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   EPP_REQUIRE(length >= 0, "negative length");
   EPP_REQUIRE(valid_len_dev && status_dev, "null result pointer");
-  EPP_REQUIRE(mode == 0 || mode == 1, "mode must be 0 or 1");
+  EPP_REQUIRE(mode >= 0 && mode <= 2, "mode must be 0, 1 or 2");
+  EPP_REQUIRE(mode != 2 || length > kCompactTile, "the wait self-test needs more than one tile of input");
   EPP_CUDA_TRY(cudaMemsetAsync(valid_len_dev, 0, sizeof(int), s));
   EPP_CUDA_TRY(cudaMemsetAsync(status_dev, 0, sizeof(int), s));
   if (length == 0) return EPP_OK;
@@ -426,6 +431,14 @@ EPP_EXPORT int eppgcn_compact_mask(const int *edge_mask, const int *col_idx, int
     compact_mask_kernel<kLookback><<<tiles, kScanThreads, 0, s>>>(edge_mask, col_idx, out_id, out_edge, length,
                                                                   tiles, hdr, desc, valid_len_dev);
     EPP_CHECK_LAUNCH("compact_mask_kernel<lookback>");
+  } else if (mode == 2) {
+    // tile ids 1 .. tiles-1 are handed out; tile 1 looks back at a descriptor nobody writes, its
+    // bounded wait runs out, the error word is set and every other tile leaves as soon as it sees it
+    skip_first_ticket_kernel<<<1, 1, 0, s>>>(hdr);
+    EPP_CHECK_LAUNCH("skip_first_ticket_kernel");
+    compact_mask_kernel<kLookback><<<tiles - 1, kScanThreads, 0, s>>>(edge_mask, col_idx, out_id, out_edge, length,
+                                                                      tiles, hdr, desc, valid_len_dev);
+    EPP_CHECK_LAUNCH("compact_mask_kernel<lookback, wait self-test>");
   } else {
     compact_mask_kernel<kCountOnly><<<tiles, kScanThreads, 0, s>>>(edge_mask, col_idx, out_id, out_edge, length,
                                                                    tiles, hdr, desc, valid_len_dev);

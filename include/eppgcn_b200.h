@@ -164,7 +164,12 @@ int eppgcn_mask_forward(const int *ids, const int *part_ptr, const int *edge_lis
  * `status_dev` (device int, may alias nothing else) receives EPP_OK or
  * EPP_ERR_SCAN_TIMEOUT when the kernels finish.
  * mode 0: one pass with a decoupled look-back scan (bounded wait);
- * mode 1: three kernels (tile counts, scan of counts, scatter), no waiting.
+ * mode 1: three kernels (tile counts, scan of counts, scatter), no waiting;
+ * mode 2: self-test of the bounded wait (length > 4096): the first tile is
+ *         withheld, so the look-back of the second one waits for a descriptor
+ *         that never comes; the wait runs out in about a second, status_dev
+ *         receives EPP_ERR_SCAN_TIMEOUT, the outputs are undefined and the
+ *         context stays usable.
  */
 size_t eppgcn_compact_scratch_bytes(int length);
 int eppgcn_compact_mask(const int *edge_mask, const int *col_idx,

@@ -129,3 +129,22 @@ def test_prepared_path_feeds_backward(cuda):
         assert valid == w["valid_len"] and parts == w["numParts"]
         assert np.array_equal(ids.cpu().numpy(), w["id"]) and np.array_equal(edges.cpu().numpy(), w["edgeList"])
         assert np.array_equal(part_ptr.cpu().numpy(), w["partPointer"])
+
+
+def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable(cuda):
+    """The look-back wait of the compaction is bounded.  Mode 2 withholds the
+    first tile, so the wait of the second one must run out: the call comes back
+    with EPP_ERR_SCAN_TIMEOUT instead of hanging, and the next call works."""
+    import time
+    rng = np.random.Generator(np.random.PCG64(1))
+    mask = np.where(rng.random(100_000) < 0.5, rng.integers(0, 1000, 100_000), -1).astype(np.int32)
+    col = rng.integers(0, 1000, 100_000).astype(np.int32)
+    t0 = time.perf_counter()
+    with pytest.raises(capi.EppError) as e:
+        capi.compact_mask(t(mask, cuda), t(col, cuda), mode=2)
+    assert e.value.status == capi.EPP_ERR_SCAN_TIMEOUT
+    assert time.perf_counter() - t0 < 30.0
+    want = O.compact_back_edge(mask, col)                      # the fallback the operator module takes
+    for mode in (1, 0):
+        ids, edges, valid = capi.compact_mask(t(mask, cuda), t(col, cuda), mode)
+        assert valid == want[2] and np.array_equal(ids.cpu().numpy(), want[0])

@@ -24,7 +24,7 @@ EXT_PATH = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
-LIB_SOURCES = ["spmm.cu", "update.cu", "prep.cu", "host.cu"]
+LIB_SOURCES = ["spmm.cu", "update.cu", "prep.cu", "exchange.cu", "host.cu"]
 
 
 def _nvcc() -> str:

@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 # EPPGCN_B200_LIB points at another build of the same library (an experimental kernel variant).
 LIB_PATH = os.environ.get("EPPGCN_B200_LIB") or os.path.join(_HERE, "libeppgcn_b200.so")
 
-EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE = range(5)
+EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE, EPP_ERR_PEER_TIMEOUT = range(6)
 
 _P, _I, _LL, _SZ = C.c_void_p, C.c_int, C.c_longlong, C.c_size_t
 
@@ -24,8 +24,8 @@ SIGNATURES = {
     "eppgcn_version": (_I, []),
     "eppgcn_status_string": (C.c_char_p, [_I]),
     "eppgcn_last_error": (C.c_char_p, []),
-    "eppgcn_spmm_forward": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
-    "eppgcn_spmm_backward_compacted": (_I, [_P, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_spmm_forward": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_spmm_backward_compacted": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
     "eppgcn_probe_gather": (_I, [_P, _LL, _P, _LL, _I, _P, _P]),
@@ -36,6 +36,8 @@ SIGNATURES = {
     "eppgcn_split_scratch_bytes": (_SZ, [_I]),
     "eppgcn_split_parts": (_I, [_P, _I, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
     "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
+    "eppgcn_push_rows": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _P]),
+    "eppgcn_peer_barrier": (_I, [_P, _I, _I, C.c_uint, _LL, _P, _P]),
     "eppgcn_build_part_host": (_I, [_I, _P, _I, _P, _P, C.POINTER(_LL)]),
     "eppgcn_map_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
     "eppgcn_bucket_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
@@ -100,6 +102,14 @@ def _row_stride(t: torch.Tensor, name: str) -> int:
     return t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
 
 
+def _out_rows(t: torch.Tensor, n: int, dim: int, name: str) -> int:
+    """Address of an ``[n, dim]`` fp32 result whose rows may be a column block of a wider matrix."""
+    _row_stride(t, name)
+    if t.size(0) < n or t.size(1) != dim:
+        raise RuntimeError(f"{name} must be [{n}, {dim}], got {list(t.shape)}")
+    return t.data_ptr()
+
+
 def update_scaled(x, w, scale=None, pad_to=8):
     """``scale[:, None] * (x @ w)`` as a view ``[N, dout]`` of a buffer whose
     row stride is ``dout`` rounded up to ``pad_to`` floats."""
@@ -134,7 +144,7 @@ def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size
         out = torch.empty(n, dim, device=feat.device, dtype=torch.float32)
     deg_row = degrees if deg_row is None else deg_row
     check(lib().eppgcn_spmm_forward(
-        _dev(out, torch.float32, "out"), feat.data_ptr(), ld,
+        _out_rows(out, n, dim, "out"), _row_stride(out, "out"), feat.data_ptr(), ld,
         _dev(row_ptr, torch.int32, "row_ptr"), _dev(col_idx, torch.int32, "col_idx"),
         _dev(deg_row, torch.float32, "deg_row"), None if prescaled else _dev(degrees, torch.float32, "degrees"),
         _dev(part_ptr, torch.int32, "part_ptr"), _dev(part2node, torch.int32, "part2node"),
@@ -151,7 +161,7 @@ def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts,
         out = torch.empty(n, dim, device=d_out.device, dtype=torch.float32)
     deg_row = degrees if deg_row is None else deg_row
     check(lib().eppgcn_spmm_backward_compacted(
-        _dev(out, torch.float32, "d_in"), d_out.data_ptr(), ld,
+        _out_rows(out, n, dim, "d_in"), _row_stride(out, "d_in"), d_out.data_ptr(), ld,
         _dev(ids, torch.int32, "ids"), _dev(part_ptr, torch.int32, "part_ptr"),
         _dev(edge_list, torch.int32, "edge_list"),
         _dev(deg_row, torch.float32, "deg_row"), _dev(degrees, torch.float32, "degrees"),
@@ -232,6 +242,30 @@ def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):
         scratch.data_ptr(), nbytes, counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
     parts, _ = _finish(counter)
     return out, parts
+
+
+def push_rows(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, dim=None):
+    """Gathers ``rows[send_idx[j]]`` and stores them into other ranks' buffers
+    (``peer_base``: their addresses as mapped into this process).  ``send_ptr``,
+    ``peer_base`` and ``peer_first_row`` are Python sequences of length
+    ``world + 1``, ``world`` and ``world``."""
+    world = len(peer_base)
+    dim = rows.size(1) if dim is None else dim
+    sp = (_LL * (world + 1))(*[int(v) for v in send_ptr])
+    pb = (_P * world)(*[int(v) if v else None for v in peer_base])
+    fr = (_LL * world)(*[int(v) for v in peer_first_row])
+    check(lib().eppgcn_push_rows(rows.data_ptr(), _row_stride(rows, "rows"), _dev(send_idx, torch.int32, "send_idx"),
+                                 sp, pb, fr, int(peer_ld), int(dim), world, _stream()))
+
+
+def peer_barrier(peer_flags, rank, value, status, max_polls=4_000_000):
+    """Enqueues barrier number ``value`` over the ranks whose flag arrays
+    (addresses as mapped into this process) are ``peer_flags``; ``status`` is a
+    device int32 that receives ``EPP_ERR_PEER_TIMEOUT`` if a wait runs out."""
+    world = len(peer_flags)
+    pf = (_P * world)(*[int(v) for v in peer_flags])
+    check(lib().eppgcn_peer_barrier(pf, int(rank), world, int(value) & 0xffffffff, int(max_polls),
+                                    _dev(status, torch.int32, "status"), _stream()))
 
 
 def count_nonzero(values) -> int:

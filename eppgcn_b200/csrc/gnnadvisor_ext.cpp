@@ -110,7 +110,7 @@ torch::Tensor aggregate_forward(const torch::Tensor &feat, const torch::Tensor &
               "part_pointers must have one more entry than part2Node");
   auto out = at::empty({n, d}, feat.options());
   const int64_t ld = n > 1 ? feat.stride(0) : std::max<int64_t>(feat.stride(0), d);
-  epp_check(eppgcn_spmm_forward(out.data_ptr<float>(), feat.data_ptr<float>(), ld,
+  epp_check(eppgcn_spmm_forward(out.data_ptr<float>(), 0, feat.data_ptr<float>(), ld,
                                 row_pointers.data_ptr<int>(), column_index.data_ptr<int>(),
                                 degrees.data_ptr<float>(), prescaled ? nullptr : degrees.data_ptr<float>(),
                                 part_pointers.data_ptr<int>(), part2Node.data_ptr<int>(),
@@ -210,7 +210,7 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
   auto d_input_prime = at::empty({n, d}, d_output.options());
   {
     ScopedTime t(2, layer);
-    epp_check(eppgcn_spmm_backward_compacted(d_input_prime.data_ptr<float>(), d_output.data_ptr<float>(), d,
+    epp_check(eppgcn_spmm_backward_compacted(d_input_prime.data_ptr<float>(), 0, d_output.data_ptr<float>(), d,
                                              id.data_ptr<int>(), partPointer.data_ptr<int>(),
                                              edgeList.data_ptr<int>(), degrees.data_ptr<float>(),
                                              degrees.data_ptr<float>(), static_cast<int>(n), static_cast<int>(d),

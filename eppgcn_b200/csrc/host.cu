@@ -89,6 +89,7 @@ EPP_EXPORT const char *eppgcn_status_string(int status) {
     case EPP_ERR_CUDA: return "EPP_ERR_CUDA";
     case EPP_ERR_SCAN_TIMEOUT: return "EPP_ERR_SCAN_TIMEOUT";
     case EPP_ERR_TOO_LARGE: return "EPP_ERR_TOO_LARGE";
+    case EPP_ERR_PEER_TIMEOUT: return "EPP_ERR_PEER_TIMEOUT";
     default: return "EPP_ERR_UNKNOWN";
   }
 }

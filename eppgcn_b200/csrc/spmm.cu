@@ -17,8 +17,11 @@
 // busy with the previous set (two slabs per warp), and the group descriptors of
 // the set after that are already on their way in registers.  Inside a set the
 // only exposed memory latency is the gather itself: a lane keeps up to eight
-// 16-byte row loads in flight, reads the column id as a shared-memory
-// broadcast and the source-side degree as a sub-warp-uniform cached load.
+// 16-byte row loads in flight and reads the column id as a shared-memory
+// broadcast.  The source-side degree is either a sub-warp-uniform cached load
+// (HASW) or absent: when the producer of the feature rows has already
+// multiplied them by the degree (deg_col == NULL), an edge costs one id and
+// one row and nothing else.
 //
 // Reduction.  After the edge loop the sub-warps of a warp that worked on the
 // same row are combined with a segmented shuffle reduction, and only the head
@@ -76,12 +79,12 @@ __device__ __forceinline__ void add_row(float *p, const float (&v)[VEC], int n, 
 }
 
 struct GroupArgs {
-  float *out;              // [num_rows][dim]
+  float *out;              // [num_rows][dim], rows out_ld floats apart
+  long long out_ld;
   const float *feat;       // rows of stride ld
   long long ld;
   const int *part_ptr;     // [num_parts+1]
   const int *row_of;       // forward: part2node[num_parts]; backward: ids[] per compacted edge
-  const int *row_ptr;      // forward only (kept for callers; the kernel derives row extents from the groups)
   const int *col;          // column id per edge
   const float *deg_row;
   const float *deg_col;
@@ -303,7 +306,7 @@ staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int 
     }
     if (m0.row >= 0 && !cont && tiles) {
       const bool whole = m0.lo != m0.row && rhi != m0.row;
-      float *dst = a.out + static_cast<long long>(m0.row) * a.dim + fcol;
+      float *dst = a.out + static_cast<long long>(m0.row) * a.out_ld + fcol;
 #pragma unroll
       for (int k = 0; k < T; ++k) {
         if ((tiles >> k) & 1u) {
@@ -377,11 +380,43 @@ int launch_shape(const GroupArgs &a, int lanes_needed, int part_size, cudaStream
   return launch_staged<VEC, 32, 8, HASW>(a, part_size, s);   // wider rows take several passes
 }
 
+// Zeroes columns 0 .. dim-1 of rows that are out_ld floats apart, W floats per store.
+template <int W>
+__global__ void __launch_bounds__(256) zero_column_block_kernel(float *out, long long out_ld, int dim, long long num_rows) {
+  const int per_row = dim / W;
+  const long long total = num_rows * per_row;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float *p = out + (i / per_row) * out_ld + (i % per_row) * W;
+    if constexpr (W == 4) *reinterpret_cast<float4 *>(p) = make_float4(0.f, 0.f, 0.f, 0.f);
+    else if constexpr (W == 2) *reinterpret_cast<float2 *>(p) = make_float2(0.f, 0.f);
+    else *p = 0.f;
+  }
+}
+
+int zero_column_block(float *out, long long out_ld, int dim, long long num_rows, cudaStream_t s) {
+  int w = 1;
+  if (dim % 4 == 0 && out_ld % 4 == 0 && aligned(out, 16)) w = 4;
+  else if (dim % 2 == 0 && out_ld % 2 == 0 && aligned(out, 8)) w = 2;
+  const long long total = num_rows * (dim / w);
+  long long blocks = ceil_div_ll(total, 256 * 4);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks < 1) blocks = 1;
+  if (w == 4) zero_column_block_kernel<4><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, out_ld, dim, num_rows);
+  else if (w == 2) zero_column_block_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, out_ld, dim, num_rows);
+  else zero_column_block_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(out, out_ld, dim, num_rows);
+  EPP_CHECK_LAUNCH("zero_column_block_kernel");
+  return EPP_OK;
+}
+
 template <bool HASW>
 int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) {
   // Dense result: rows that no group touches, and rows that are accumulated
   // with atomics, start from zero.
-  EPP_CUDA_TRY(cudaMemsetAsync(a.out, 0, sizeof(float) * static_cast<size_t>(num_rows) * a.dim, s));
+  if (a.out_ld == a.dim)
+    EPP_CUDA_TRY(cudaMemsetAsync(a.out, 0, sizeof(float) * static_cast<size_t>(num_rows) * a.dim, s));
+  else if (const int rc = zero_column_block(a.out, a.out_ld, a.dim, num_rows, s); rc != EPP_OK)
+    return rc;
   if (a.num_parts == 0) return EPP_OK;
   if (a.ld > 0x3fffffffLL) {
     set_error("row stride too large");
@@ -392,8 +427,8 @@ int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) 
   if (a.ld % 4 == 0 && aligned(a.feat, 16) && a.ld >= ((a.dim + 3) / 4) * 4) vec = 4;
   else if (a.ld % 2 == 0 && aligned(a.feat, 8) && a.ld >= ((a.dim + 1) / 2) * 2) vec = 2;
   a.ovec = 1;
-  if (a.dim % 4 == 0 && aligned(a.out, 16)) a.ovec = 4;
-  else if (a.dim % 2 == 0 && aligned(a.out, 8)) a.ovec = 2;
+  if (a.out_ld % 4 == 0 && aligned(a.out, 16)) a.ovec = 4;
+  else if (a.out_ld % 2 == 0 && aligned(a.out, 8)) a.ovec = 2;
   const int lanes_needed = (a.dim + vec - 1) / vec;
   switch (vec) {
     case 4:  return launch_shape<4, HASW>(a, lanes_needed, part_size, s);
@@ -465,7 +500,7 @@ EPP_EXPORT int eppgcn_probe_gather(const int *col_idx, long long num_edges, cons
   return EPP_OK;
 }
 
-EPP_EXPORT int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
+EPP_EXPORT int eppgcn_spmm_forward(float *out, long long out_ld, const float *feat, long long feat_ld,
                                    const int *row_ptr, const int *col_idx,
                                    const float *deg_row, const float *deg_col,
                                    const int *part_ptr, const int *part2node,
@@ -475,18 +510,19 @@ EPP_EXPORT int eppgcn_spmm_forward(float *out, const float *feat, long long feat
   (void)dim_worker; (void)warp_per_block;
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(feat_ld >= dim, "feat_ld must be >= dim");
+  EPP_REQUIRE(out_ld == 0 || out_ld >= dim, "out_ld must be 0 or >= dim");
   if (num_nodes == 0) return EPP_OK;
   EPP_REQUIRE(out && feat && row_ptr && deg_row, "null pointer");
   EPP_REQUIRE(num_parts == 0 || (col_idx && part_ptr && part2node), "null pointer");
   epp::GroupArgs a{};
-  a.out = out; a.feat = feat; a.ld = feat_ld;
-  a.part_ptr = part_ptr; a.row_of = part2node; a.row_ptr = row_ptr; a.col = col_idx;
+  a.out = out; a.out_ld = out_ld ? out_ld : dim; a.feat = feat; a.ld = feat_ld;
+  a.part_ptr = part_ptr; a.row_of = part2node; a.col = col_idx;
   a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim; a.bwd = 0;
   return deg_col ? epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream))
                  : epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));
 }
 
-EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
+EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *d_out, long long d_out_ld,
                                               const int *ids, const int *part_ptr, const int *edge_list,
                                               const float *deg_row, const float *deg_col,
                                               int num_nodes, int dim, int num_parts,
@@ -495,12 +531,13 @@ EPP_EXPORT int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, l
   (void)blockx; (void)blocky;
   EPP_REQUIRE(num_nodes >= 0 && dim >= 1 && num_parts >= 0, "negative size or dim < 1");
   EPP_REQUIRE(d_out_ld >= dim, "d_out_ld must be >= dim");
+  EPP_REQUIRE(d_in_ld == 0 || d_in_ld >= dim, "d_in_ld must be 0 or >= dim");
   if (num_nodes == 0) return EPP_OK;
   EPP_REQUIRE(d_in && d_out && deg_row, "null pointer");
   EPP_REQUIRE(num_parts == 0 || (ids && part_ptr && edge_list), "null pointer");
   epp::GroupArgs a{};
-  a.out = d_in; a.feat = d_out; a.ld = d_out_ld;
-  a.part_ptr = part_ptr; a.row_of = ids; a.row_ptr = nullptr; a.col = edge_list;
+  a.out = d_in; a.out_ld = d_in_ld ? d_in_ld : dim; a.feat = d_out; a.ld = d_out_ld;
+  a.part_ptr = part_ptr; a.row_of = ids; a.col = edge_list;
   a.deg_row = deg_row; a.deg_col = deg_col; a.num_parts = num_parts; a.dim = dim; a.bwd = 1;
   return deg_col ? epp::launch_group_spmm<true>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream))
                  : epp::launch_group_spmm<false>(a, num_nodes, part_size, static_cast<cudaStream_t>(stream));

@@ -1,8 +1,28 @@
 """Row-partitioned data parallelism for the GCN aggregation hot path.
 
 The reference is single-GPU.  Destination rows are independent once the whole
-source matrix is visible, so the graph is cut into contiguous
-destination-vertex ranges with (nearly) equal edge counts, one range per rank:
+source matrix is visible, so every rank owns a set of destination rows.  Three
+ways of choosing and exchanging them are kept, selected by ``exchange``:
+
+  ``balanced``   (default) vertices are relabelled by a degree-sorted round robin,
+                 so that every rank owns the same number of rows and (nearly) the
+                 same number of edges; equal blocks make the row exchange a plain
+                 ``all_gather_into_tensor``, and the backward pass gathers only the
+                 rows the execution path marks (``MaskedGather``).
+  ``allgather``  contiguous vertex ranges with (nearly) equal edge counts; blocks
+                 are uneven, so the exchange pads to the largest one.
+  ``halo``       contiguous ranges, but only the rows a rank's edges touch travel
+                 (``HaloPlan``, all-to-all); least traffic, slowest in practice.
+  ``columns``    every rank keeps the whole graph and aggregates ``D / world``
+                 feature columns of every row: an all-to-all turns the rank's row
+                 block of the source matrix into its column slice of all rows, the
+                 SpMM runs over the full edge list on that slice, and a second
+                 all-to-all turns the result back into row blocks.  A rank sends
+                 and receives ``2 N D / world`` floats per aggregation instead of
+                 the ``N D (world - 1) / world`` of a row all-gather, and no rank
+                 depends on how the edges are spread over the rows.
+
+Per layer, in the row-partitioned modes:
 
   forward, per layer    local ``X_g @ W`` -> all-gather of the (narrow) post-update
                         rows into every rank's own memory -> local SpMM over the
@@ -186,6 +206,38 @@ def _padded_rows(t: torch.Tensor) -> torch.Tensor:
     return t if ld == t.size(1) else torch.as_strided(t, (t.size(0), ld), (ld, 1), t.storage_offset())
 
 
+def rows_to_column_slice(local: torch.Tensor, send: torch.Tensor, src: torch.Tensor, group=None):
+    """This rank's row block ``local [n_loc, d]`` of a matrix -> its column slice
+    ``src [world * n_loc, ceil(d / world)]`` of all rows.  ``send [world, n_loc,
+    ceil(d / world)]`` stages the block-major copy: block ``b`` holds the columns
+    rank ``b`` owns and is what rank ``b`` receives as its rows ``rank * n_loc ..``.
+    With a ragged last block the padding columns of ``send`` must be zero."""
+    w, ds_, d = send.size(0), send.size(2), local.size(1)
+    if d == w * ds_:
+        send.copy_(local.unflatten(1, (w, ds_)).transpose(0, 1))
+    else:
+        for b in range(-(-d // ds_)):
+            hi = min((b + 1) * ds_, d)
+            send[b, :, :hi - b * ds_].copy_(local[:, b * ds_:hi])
+    dist.all_to_all_single(src.view(-1), send.view(-1), group=group)
+    return src
+
+
+def column_slice_to_rows(agg: torch.Tensor, recv: torch.Tensor, local: torch.Tensor, group=None):
+    """Inverse of :func:`rows_to_column_slice`: ``agg [world * n_loc, ds]`` (this
+    rank's columns of all rows; rank ``b``'s rows are one contiguous block, so it
+    is the send buffer as it stands) -> ``local [n_loc, d]``."""
+    w, ds_, d = recv.size(0), recv.size(2), local.size(1)
+    dist.all_to_all_single(recv.view(-1), agg.view(-1), group=group)
+    if d == w * ds_:
+        local.unflatten(1, (w, ds_)).copy_(recv.transpose(0, 1))
+    else:
+        for b in range(-(-d // ds_)):
+            hi = min((b + 1) * ds_, d)
+            local[:, b * ds_:hi].copy_(recv[b, :, :hi - b * ds_])
+    return local
+
+
 class HaloPlan:
     """Exchange of only the source rows a rank's edges reference.
 
@@ -234,6 +286,165 @@ class HaloPlan:
         buf = torch.empty(self.num_rows, rows.size(1), dtype=local.dtype, device=local.device)
         dist.all_to_all_single(buf, send, self.recv_counts, self.send_counts, group=self.group)
         return buf[:, :local.size(1)]
+
+
+class PeerFabric:
+    """Peer-mapped buffers of the ranks of one node and a flag barrier over them.
+
+    Buffers come from torch's symmetric-memory allocator, which maps every
+    rank's copy into every process; only this package's own kernels
+    (``eppgcn_push_rows``, ``eppgcn_peer_barrier``) ever touch a peer's copy --
+    plain stores and flag words, no library kernel is handed a peer address.
+    Every barrier wait is bounded; :meth:`check` raises if one ran out."""
+
+    def __init__(self, dev, rank: int, world: int, group=None, max_polls: int = 10_000_000):
+        import torch.distributed._symmetric_memory as symm
+        from eppgcn_b200 import capi
+        self.symm, self.capi = symm, capi
+        self.dev, self.rank, self.world = dev, rank, world
+        self.group = group if group is not None else dist.group.WORLD
+        self._keep = []
+        flags, self.flag_ptrs = self.alloc((64,), torch.int32)
+        flags.zero_()
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.count, self.max_polls = 0, max_polls    # a poll takes about a microsecond: ranks may be ~10 s apart
+        torch.cuda.synchronize(dev)
+        dist.barrier(self.group)                     # every rank's flag words are zero before the first barrier
+
+    def alloc(self, shape, dtype=torch.float32):
+        """A buffer of the same shape on every rank; returns ``(own tensor, [address of rank r's copy])``."""
+        t = self.symm.empty(tuple(shape), dtype=dtype, device=self.dev)
+        hdl = self.symm.rendezvous(t, self.group)
+        peers = [hdl.get_buffer(r, tuple(shape), dtype) for r in range(self.world)]
+        self._keep.append((t, hdl, peers))
+        return t, [p.data_ptr() for p in peers]
+
+    def barrier(self):
+        self.count += 1
+        self.capi.peer_barrier(self.flag_ptrs, self.rank, self.count, self.status, self.max_polls)
+
+    def check(self):
+        code = int(self.status.item())
+        if code != 0:
+            raise RuntimeError(f"a bounded wait for another GPU ran out (status {code}): a rank is late or gone")
+
+
+class DealtHalo:
+    """Halo exchange over equal row blocks (the dealt-out relabelling), with the
+    rank's own rows kept out of the all-to-all and the transfer cut into column
+    chunks so that the aggregation of one chunk runs while the next one travels.
+
+    The source buffer of chunk ``c`` is ``[num_remote + n_loc, d / chunks]``:
+    first the remote rows this rank's edges reference, sorted by global id (hence
+    grouped by owner), then the rank's own ``n_loc`` rows.  ``remap`` gives every
+    edge its row in that buffer; ``order`` lists the global ids in buffer order.
+    """
+
+    def __init__(self, cols: torch.Tensor, n_loc: int, rank: int, world: int, group=None, fabric=None):
+        dev = cols.device
+        self.rank, self.world, self.group, self.n_loc = rank, world, group, n_loc
+        self.fabric = fabric if world > 1 else None
+        ids = cols.long()
+        v0 = rank * n_loc
+        own = (ids >= v0) & (ids < v0 + n_loc)
+        remote_ids = ids[~own]
+        self.needed = torch.unique(remote_ids)                             # sorted global ids of other ranks' rows
+        r = int(self.needed.numel())
+        remap = torch.empty_like(ids)
+        remap[~own] = torch.searchsorted(self.needed, remote_ids)
+        remap[own] = ids[own] - v0 + r
+        self.remap = remap.to(torch.int32)
+        b = torch.arange(world + 1, device=dev, dtype=torch.int64) * n_loc
+        cut = torch.searchsorted(self.needed, b)
+        counts_in = cut[1:] - cut[:-1]
+        self.recv_counts = counts_in.tolist()
+        request = self.needed % n_loc                                      # row ids local to their owner
+        counts_out = torch.empty_like(counts_in)
+        if world > 1:
+            dist.all_to_all_single(counts_out, counts_in, group=group)
+        else:
+            counts_out.copy_(counts_in)
+        self.send_counts = counts_out.tolist()
+        self.send_idx = torch.empty(int(sum(self.send_counts)), dtype=torch.int64, device=dev)
+        if world > 1:
+            dist.all_to_all_single(self.send_idx, request, self.send_counts, self.recv_counts, group=group)
+        self.num_remote, self.num_rows = r, r + n_loc
+        self.order = torch.cat([self.needed, torch.arange(v0, v0 + n_loc, device=dev)])
+        self._bufs = {}
+        if self.fabric is not None:
+            # peer stores: where this rank's rows start in every reader's buffer, and one buffer size for all ranks
+            first_in = cut[:-1].clone()
+            first_out = torch.empty_like(first_in)
+            dist.all_to_all_single(first_out, first_in, group=group)
+            self.peer_first_row = first_out.tolist()
+            self.send_ptr = [0] + np.cumsum(self.send_counts).tolist()
+            self.send_idx32 = self.send_idx.to(torch.int32)
+            rows_max = torch.tensor([self.num_rows], device=dev, dtype=torch.int64)
+            dist.all_reduce(rows_max, op=dist.ReduceOp.MAX, group=group)
+            self.rows_max = int(rows_max.item())
+
+    def buffers(self, d: int, chunks: int):
+        """Per-chunk (send rows, source buffer) pairs for a ``d``-wide matrix; the
+        chunk count falls back to 1 when ``d`` does not split into 16-byte aligned rows."""
+        if chunks < 1 or d % (4 * chunks):
+            chunks = 1
+        key = (d, chunks)
+        if key not in self._bufs:
+            dc = d // chunks
+            dev = self.send_idx.device
+            if self.fabric is not None:
+                ld = (dc + 3) // 4 * 4               # rows travel as whole 16-byte pieces; padding stays zero
+                made = []
+                for _ in range(chunks):
+                    whole, peers = self.fabric.alloc((self.rows_max, ld))
+                    whole.zero_()
+                    made.append((peers, whole[:self.num_rows, :dc]))
+                self._bufs[key] = made
+            else:
+                self._bufs[key] = [(torch.empty(self.send_idx.numel(), dc, device=dev),
+                                    torch.zeros(self.num_rows, dc, device=dev)) for _ in range(chunks)]
+        return self._bufs[key]
+
+    def own_rows(self, d: int, chunks: int = 1):
+        """The places of the rank's own rows inside the source buffers, one
+        ``[n_loc, d / chunks]`` view per chunk.  A producer that writes its rows
+        there (column block by column block) saves the copy :meth:`start` makes."""
+        return [buf[self.num_remote:] for _, buf in self.buffers(d, chunks)]
+
+    def start(self, local, chunks: int = 1, d: int = 0):
+        """Enqueues the exchange of ``local [n_loc, d]``, one all-to-all per column
+        chunk; ``local = None``: the rows already sit in :meth:`own_rows` (``d``
+        names the width).  Returns ``[(work, buffer)]``; ``work.wait()`` makes the
+        current stream wait for that chunk only."""
+        d = local.size(1) if local is not None else d
+        out = []
+        bufs = self.buffers(d, chunks)
+        if self.fabric is not None and isinstance(bufs[0][0], list):
+            # peer stores: wait until no rank reads these buffers any more, push, wait until every push has landed
+            self.fabric.barrier()
+            for c, (peers, buf) in enumerate(bufs):
+                dc = buf.size(1)
+                own = buf[self.num_remote:]
+                if local is not None:
+                    own.copy_(local[:, c * dc:(c + 1) * dc])
+                wide = _padded_rows(own)
+                self.fabric.capi.push_rows(wide, self.send_idx32, self.send_ptr, peers, self.peer_first_row,
+                                           wide.size(1))
+                out.append((None, buf))
+            self.fabric.barrier()
+            return out
+        for c, (send, buf) in enumerate(bufs):
+            dc = send.size(1)
+            if local is not None:
+                buf[self.num_remote:].copy_(local[:, c * dc:(c + 1) * dc])
+            part = buf[self.num_remote:]
+            work = None
+            if self.world > 1 and self.num_remote + send.size(0) > 0:
+                torch.index_select(part, 0, self.send_idx, out=send)
+                work = dist.all_to_all_single(buf[:self.num_remote], send, self.recv_counts, self.send_counts,
+                                              group=self.group, async_op=True)
+            out.append((work, buf))
+        return out
 
 
 class MaskedGather:
@@ -287,19 +498,29 @@ class DistHotPath:
     ``"halo"``       same ranges, only referenced rows travel (all-to-all); least
                      bytes, but NCCL send/recv was the slowest of the three on
                      8 x B200 for this graph.
+    ``"balanced_halo"``  the relabelling of ``balanced`` with the exchange of
+                     ``halo``: the dealt-out rows make the per-pair row counts of
+                     the all-to-all nearly equal, and only referenced rows travel.
+    ``"columns"``    whole graph on every rank, ``ceil(D / world)`` feature columns
+                     each; two equal-split all-to-alls per aggregation.
     """
 
     def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None,
-                 exchange: str = "balanced"):
+                 exchange: str = "balanced", chunks: int = 1, transport: str = "push"):
         import eppgcn_b200
         from eppgcn_b200 import capi
         self.capi, self.dev, self.rank, self.world, self.group = capi, dev, rank, world, group
-        self.mode = exchange
+        self.mode, self.chunks, self.fabric = exchange, chunks, None
         gnna = eppgcn_b200.load_gnnadvisor()
         on_device = torch.is_tensor(getattr(ds, "indptr", None))      # DeviceWorkload: the graph never touches the host
+        if exchange == "columns":
+            self._init_columns(ds, gnna, on_device, back_size)
+            return
+        relabel = exchange in ("balanced", "balanced_halo")
+        halo = exchange in ("halo", "balanced_halo")
         if on_device:
-            if exchange != "balanced":
-                raise ValueError("device-resident workloads support the balanced mode only")
+            if not relabel:
+                raise ValueError("device-resident workloads support the balanced, balanced_halo and columns modes")
             new_of_old, n_loc, local_ptr, cols = balanced_shard_device(ds.indptr, ds.indices, rank, world)
             self.new_of_old = new_of_old
             self.n = n_loc * world
@@ -315,7 +536,7 @@ class DistHotPath:
             degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
         if on_device:
             pass
-        elif exchange == "balanced":
+        elif relabel:
             # relabelled graph: equal rows per rank, hubs dealt out; every per-vertex array follows the new ids
             self.new_of_old, n_loc = balanced_relabel(g.indptr, world)
             self.n = n_loc * world
@@ -342,6 +563,7 @@ class DistHotPath:
         self.deg = deg_t if on_device else torch.from_numpy(degrees_np).to(dev)
         self.deg_row = self.deg[sh.v0:sh.v1]
         n_loc, e_loc = sh.num_rows, sh.num_edges
+        self.n_loc = n_loc
         train = train_t if on_device else torch.from_numpy(train_np).to(dev)
         ngh = [torch.zeros(self.n, dtype=torch.bool, device=dev) for _ in range(L - 1)]
         edge_masks = [torch.full((e_loc,), -1, dtype=torch.int32, device=dev) for _ in range(L)]
@@ -377,7 +599,22 @@ class DistHotPath:
                 p.update(plan=plan, edges_c=edges_c, deg_c=plan.compact(self.deg, 0.0))
             torch.cuda.synchronize(dev)
             self.plan_s = time.perf_counter() - t0
-        if exchange == "halo":
+        if exchange == "balanced_halo":
+            t0 = time.perf_counter()
+            if transport not in ("push", "nccl"):
+                raise ValueError("transport must be 'push' (peer stores by this package's kernels) or 'nccl'")
+            if transport == "push" and world > 1 and dev.type == "cuda" and dist.get_backend(group) == "nccl":
+                self.fabric = PeerFabric(dev, rank, world, group)
+            self.fwd_plan = DealtHalo(self.col, n_loc, rank, world, group, self.fabric)
+            self.col_c = self.fwd_plan.remap
+            for p in self.path:
+                plan = DealtHalo(p["edges"][:p["valid"]], n_loc, rank, world, group, self.fabric)
+                edges_c = torch.zeros_like(p["edges"])
+                edges_c[:p["valid"]] = plan.remap
+                p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.order].contiguous())
+            torch.cuda.synchronize(dev)
+            self.plan_s = time.perf_counter() - t0
+        elif halo:
             t0 = time.perf_counter()
             self.fwd_plan = HaloPlan(self.col, self.bounds, rank, world, group)
             self.col_c = self.fwd_plan.remap
@@ -388,6 +625,89 @@ class DistHotPath:
                 p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.needed].contiguous())
             torch.cuda.synchronize(dev)
             self.plan_s = time.perf_counter() - t0
+
+    def _init_columns(self, ds, gnna, on_device, back_size):
+        """Whole graph on this rank; the execution path is prepared locally, with
+        no mask exchange, exactly as on one GPU."""
+        capi, dev, world = self.capi, self.dev, self.world
+        if on_device:
+            indptr, col = ds.indptr.to(torch.int32), ds.indices
+            deg, train = ds.degrees.to(dev), ds.train_mask.to(dev)
+        else:
+            g = ds.graph
+            indptr = torch.from_numpy(g.indptr).to(dev, torch.int32)
+            col = torch.from_numpy(g.indices).to(dev, torch.int32)
+            deg, train = ds.degrees.to(dev), ds.train_mask.to(dev)
+        n = indptr.numel() - 1
+        n_loc = -(-n // world)
+        n_pad = n_loc * world
+        if n_pad > n:                               # empty rows fill the last rank's block
+            indptr = torch.cat([indptr, indptr[-1:].expand(n_pad - n)])
+            deg = torch.cat([deg, torch.ones(n_pad - n, device=dev)])
+            train = torch.cat([train, torch.zeros(n_pad - n, dtype=torch.bool, device=dev)])
+        self.n, self.n_loc, self.new_of_old = n_pad, n_loc, None
+        self.bounds = np.arange(world + 1, dtype=np.int64) * n_loc
+        self.part_size = max(int(ds.avg_degree), 1)
+        row_cpu = indptr.cpu()
+        self.shard = RowShard(self.rank, 0, n_pad, row_cpu, col)
+        pp, p2n = gnna.build_part(self.part_size, row_cpu)
+        self.row, self.col, self.pp, self.p2n = indptr.contiguous(), col, pp.to(dev), p2n.to(dev)
+        self.deg = self.deg_row = deg.contiguous()
+        L, e = ds.num_layers, col.numel()
+        ngh = [torch.zeros(n_pad, dtype=torch.bool, device=dev) for _ in range(L - 1)]
+        node_degs = [torch.zeros(n_pad, dtype=torch.int32, device=dev) for _ in range(L)]
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        self.path = [None] * L
+        for i in range(L):
+            j = L - 1 - i
+            edge_mask = torch.full((e,), -1, dtype=torch.int32, device=dev)
+            capi.mask_forward(self.p2n, self.pp, self.col, train if i == 0 else ngh[i - 1],
+                              ngh[i] if i < L - 1 else None, edge_mask, node_degs[j], L, i + 1)
+            ids, edges, valid = capi.compact_mask(edge_mask, self.col)
+            del edge_mask
+            ids, edges = ids[:valid].clone(), edges[:valid].clone()      # keep only the marked part resident
+            ppb, parts = capi.split_parts(node_degs[j], e, back_size)
+            self.path[j] = dict(id=ids, edges=edges, pp=ppb[:parts + 1].clone(), parts=parts, valid=valid,
+                                rows=int(torch.count_nonzero(node_degs[j]).item()))
+        torch.cuda.synchronize(dev)
+        self.prep_s = time.perf_counter() - t0
+        self.ngh_masks, self.node_degs, self.back_size = ngh, node_degs, back_size
+        self._cols = {}
+
+    def col_slice(self, d: int) -> int:
+        """Feature columns per rank for a ``d``-wide matrix."""
+        return -(-d // self.world)
+
+    def _column_buffers(self, key, d):
+        """Per-aggregation buffers: block-major send rows, the column slice of all
+        rows before and after the SpMM, block-major received rows."""
+        if key not in self._cols:
+            w, ds_ = self.world, self.col_slice(d)
+            mk = lambda *shape: torch.zeros(*shape, device=self.dev)
+            self._cols[key] = dict(send=mk(w, self.n_loc, ds_), src=mk(self.n, ds_), agg=mk(self.n, ds_),
+                                   recv=mk(w, self.n_loc, ds_))
+        return self._cols[key]
+
+    def columns_local(self, key, kind, i, d):
+        """The SpMM of one aggregation on this rank's column slice of all rows."""
+        b = self._column_buffers(key, d)
+        if kind == "fwd":
+            return self.capi.spmm_forward(b["src"], self.row, self.col, self.deg, self.pp, self.p2n, self.part_size,
+                                          out=b["agg"], prescaled=True)
+        p = self.path[i]
+        return self.capi.spmm_backward_compacted(b["src"], p["id"], p["pp"], p["edges"], self.deg, p["parts"],
+                                                 self.back_size, out=b["agg"], num_rows=self.n)
+
+    def columns_op(self, key, kind, i, local_in, out_local):
+        """One aggregation in the ``columns`` mode: row block -> column slice
+        (all-to-all), SpMM over the whole graph, column slice -> row block."""
+        d = local_in.size(1)
+        b = self._column_buffers(key, d)
+        rows_to_column_slice(local_in, b["send"], b["src"], self.group)
+        self.columns_local(key, kind, i, d)
+        column_slice_to_rows(b["agg"], b["recv"], out_local, self.group)
+        return out_local
 
     def gather(self, full, local):
         return all_gather_rows(full, local, self.bounds, self.group)
@@ -403,14 +723,53 @@ class DistHotPath:
                                                  self.back_size, out=out_local, deg_row=self.deg_row,
                                                  num_rows=self.shard.num_rows)
 
+    def _halo_spmm(self, kind, i, buf, out):
+        if kind == "fwd":
+            return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
+                                          out=out, deg_row=self.deg_row, prescaled=True)
+        p = self.path[i]
+        return self.capi.spmm_backward_compacted(buf, p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
+                                                 self.back_size, out=out, deg_row=self.deg_row,
+                                                 num_rows=self.shard.num_rows)
+
+    def _dealt_op(self, kind, i, local, out_local):
+        """Chunked exchange + aggregation: chunk ``c`` is aggregated (straight into
+        its column block of ``out_local``) while chunk ``c + 1`` travels."""
+        plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
+        pending = plan.start(local, self.chunks, out_local.size(1))
+        dc = out_local.size(1) // len(pending)
+        for c, (work, buf) in enumerate(pending):
+            if work is not None:
+                work.wait()
+            self._halo_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc])
+        return out_local
+
+    def halo_inputs(self, kind, i, d):
+        """Where the producer of an aggregation's input puts this rank's rows (see
+        :meth:`DealtHalo.own_rows`); pass ``None`` as the input afterwards."""
+        plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
+        return plan.own_rows(d, self.chunks)
+
+    def halo_local(self, kind, i, out_local):
+        """Only the aggregation kernels of one operation, on the buffers the last exchange filled."""
+        plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
+        bufs = plan.buffers(out_local.size(1), self.chunks)
+        dc = out_local.size(1) // len(bufs)
+        for c, (_, buf) in enumerate(bufs):
+            self._halo_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc])
+
     def forward_halo(self, local, out_local):
         """Exchange of the referenced (pre-scaled) source rows, then the local forward aggregation."""
+        if isinstance(self.fwd_plan, DealtHalo):
+            return self._dealt_op("fwd", 0, local, out_local)
         buf = self.fwd_plan.exchange(local)
         return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
                                       out=out_local, deg_row=self.deg_row, prescaled=True)
 
     def backward_halo(self, i, d_out_local, out_local):
         p = self.path[i]
+        if isinstance(p["plan"], DealtHalo):
+            return self._dealt_op("bwd", i, d_out_local, out_local)
         buf = p["plan"].exchange(d_out_local)
         return self.capi.spmm_backward_compacted(buf, p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
                                                  self.back_size, out=out_local, deg_row=self.deg_row,
@@ -444,25 +803,40 @@ def run_bench(args, rank: int, world: int, dev):
             ds = graphs.load_workload(args.workload, args.seed)
     n, e, L = ds.num_nodes, ds.num_edges, ds.num_layers
     dims = [spec["hidden"]] * (L - 1) + [spec["classes"]]
-    mode = "balanced" if device_drawn else getattr(args, "exchange", "balanced")
-    halo = mode == "halo"
-    hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode)
+    mode = getattr(args, "exchange", "balanced")
+    if device_drawn and mode not in ("balanced", "balanced_halo", "columns"):
+        mode = "balanced"
+    halo, columns = mode in ("halo", "balanced_halo"), mode == "columns"
+    hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=getattr(args, "chunks", 1),
+                     transport=getattr(args, "transport", "push"))
+    dealt = mode == "balanced_halo"
     if device_drawn:
         ds.indptr = ds.indices = None           # the shard is all this rank needs from here on
         torch.cuda.empty_cache()
     setup_s = time.perf_counter() - t0
-    n_loc = hp.shard.num_rows
+    n_loc = hp.n_loc
     gen = torch.Generator(device=dev).manual_seed(args.seed + rank)
     # operations of one epoch: forward of every layer, then backward from the last layer down
     ops = [("fwd", i, dims[i]) for i in range(L)] + [("bwd", i, dims[i]) for i in reversed(range(L))]
     # forward inputs as the update step leaves them (padded rows), backward inputs as autograd does (dense)
-    local_in = [B.padded(n_loc, d, dev, gen) if kind == "fwd" else torch.randn(n_loc, d, device=dev, generator=gen)
-                for kind, _, d in ops]
+    if dealt:
+        # the producer of an input writes this rank's rows straight into the exchange buffers
+        local_in = [None] * len(ops)
+        staged = [hp.halo_inputs(kind, i, d) for kind, i, d in ops]
+        for views in staged:
+            for v in views:
+                v.normal_(generator=gen)
+    else:
+        local_in = [B.padded(n_loc, d, dev, gen) if kind == "fwd" else torch.randn(n_loc, d, device=dev, generator=gen)
+                    for kind, _, d in ops]
+        staged = [[x] for x in local_in]
     outs = [torch.empty(n_loc, d, device=dev) for _, _, d in ops]
     compact_bwd = "plan" in hp.path[0]
     full = [None] * len(ops)
     bufs = [None] * len(ops)
     for k, (kind, i, d) in enumerate(ops):
+        if columns or dealt:
+            continue                                  # these modes keep their own per-aggregation buffers
         if halo:
             bufs[k] = (hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).exchange(local_in[k])
         elif kind == "bwd" and compact_bwd:
@@ -471,8 +845,10 @@ def run_bench(args, rank: int, world: int, dev):
             full[k] = B.padded(hp.n, d, dev, gen) if kind == "fwd" else torch.empty(hp.n, d, device=dev)
 
     def one(k):
-        kind, i, _ = ops[k]
-        if kind == "bwd" and compact_bwd:
+        kind, i, d = ops[k]
+        if columns:
+            hp.columns_op(k, kind, i, local_in[k], outs[k])
+        elif kind == "bwd" and compact_bwd:
             hp.backward_halo(i, local_in[k], outs[k])
         elif halo:
             hp.forward_halo(local_in[k], outs[k])
@@ -481,7 +857,11 @@ def run_bench(args, rank: int, world: int, dev):
             (hp.forward(full[k], outs[k]) if kind == "fwd" else hp.backward(i, full[k], outs[k]))
 
     def local_only(k):
-        kind, i, _ = ops[k]
+        kind, i, d = ops[k]
+        if columns:
+            return hp.columns_local(k, kind, i, d)
+        if dealt:
+            return hp.halo_local(kind, i, outs[k])
         if kind == "fwd":
             if not halo:
                 return hp.forward(full[k], outs[k])
@@ -502,6 +882,8 @@ def run_bench(args, rank: int, world: int, dev):
         for _ in range(max(args.warmup, 3)):
             step()
         torch.cuda.synchronize()
+        if hp.fabric is not None:
+            hp.fabric.check()
         dist.barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
@@ -524,14 +906,17 @@ def run_bench(args, rank: int, world: int, dev):
         kms = torch.tensor([k0.elapsed_time(k1) / args.steps], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     dist.all_reduce(kms, op=dist.ReduceOp.MAX)
+    if hp.fabric is not None:
+        hp.fabric.check()
 
     # e2e: host buffers, every step stages this rank's rows in and its results out
-    host_in = [torch.empty(x.shape, pin_memory=True).copy_(x) for x in local_in]
+    host_in = [[torch.empty(x.shape, pin_memory=True).copy_(x) for x in views] for views in staged]
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
 
     def e2e_step():
         for k in range(len(ops)):
-            local_in[k].copy_(host_in[k], non_blocking=True)
+            for x, h in zip(staged[k], host_in[k]):
+                x.copy_(h, non_blocking=True)
             one(k)
             host_out[k].copy_(outs[k], non_blocking=True)
 
@@ -547,7 +932,7 @@ def run_bench(args, rank: int, world: int, dev):
     torch.cuda.synchronize()
     e2e = torch.tensor([ev0.elapsed_time(ev1) / steps2], device=dev)
     dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
-    byts = torch.tensor([sum(x.numel() * 4 for x in local_in), sum(o.numel() * 4 for o in outs)],
+    byts = torch.tensor([sum(x.numel() * 4 for views in staged for x in views), sum(o.numel() * 4 for o in outs)],
                         device=dev, dtype=torch.int64)
     dist.all_reduce(byts)
     edges = torch.tensor([hp.shard.num_edges, n_loc], device=dev, dtype=torch.int64)
@@ -556,6 +941,8 @@ def run_bench(args, rank: int, world: int, dev):
     if rank == 0:
         peak, peak_src = B.measured_peak_gbs()
         exchanged = [(bufs[k].size(0) if bufs[k] is not None else hp.n) for k in range(len(ops))]
+        if dealt:
+            exchanged = [(hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).num_remote for kind, i, _ in ops]
         line = {
             "metric": f"{L}-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms.item(), 4),
             "unit": "ms/epoch", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
@@ -570,6 +957,17 @@ def run_bench(args, rank: int, world: int, dev):
                                       + {"halo": "contiguous ranges, one NCCL all-to-all of the referenced source "
                                                  "rows per aggregation",
                                          "allgather": "contiguous ranges, one uneven NCCL row all-gather per aggregation",
+                                         "balanced_halo": "degree-dealt relabelling (equal rows and edges per "
+                                                          "rank), NCCL all-to-all of the referenced remote source "
+                                                          f"rows in {hp.chunks} column chunk(s) per aggregation, "
+                                                          + ("gathered and stored into the readers' buffers over "
+                                                             "NVLink by one kernel of this library, flag barriers "
+                                                             "with bounded waits" if hp.fabric is not None else
+                                                             "NCCL all-to-all"),
+                                         "columns": "whole graph on every rank, ceil(D/world) feature columns each; "
+                                                    "two equal-split NCCL all-to-alls per aggregation (row block "
+                                                    "-> column slice -> row block), layout copies inside the timed "
+                                                    "region",
                                          "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
                                                      "NCCL all-gather per aggregation (source-mask rows only for "
                                                      "the backward layers)"}[mode]},

@@ -26,7 +26,8 @@ enum {
   EPP_ERR_BAD_ARG = 1,       /* null pointer, negative size, part size < 1 ...      */
   EPP_ERR_CUDA = 2,          /* a CUDA runtime call or launch failed                  */
   EPP_ERR_SCAN_TIMEOUT = 3,  /* the bounded look-back wait of a scan kernel ran out  */
-  EPP_ERR_TOO_LARGE = 4      /* a size is beyond what the entry point supports       */
+  EPP_ERR_TOO_LARGE = 4,     /* a size is beyond what the entry point supports       */
+  EPP_ERR_PEER_TIMEOUT = 5   /* the bounded wait for another GPU's flag ran out      */
 };
 
 /* Library version as major*10000 + minor*100 + patch. */
@@ -47,6 +48,10 @@ const char *eppgcn_last_error(void);
  *
  * out       [num_nodes][dim] dense fp32, fully overwritten (rows without
  *           edges come back zero).
+ * out       fp32 rows with a stride of out_ld floats (out_ld >= dim, or 0
+ *           for a dense [num_nodes][dim] result); columns beyond dim are
+ *           left untouched, so a caller can fill a column block of a wider
+ *           matrix.
  * feat      fp32 rows with a stride of feat_ld floats (feat_ld >= dim).
  * row_ptr   [num_nodes+1], col_idx [row_ptr[num_nodes]]  int32 CSR.
  * deg_row / deg_col   per-vertex factors of the destination and the source
@@ -62,7 +67,7 @@ const char *eppgcn_last_error(void);
  *           (EPPGCN/param.py:80-124).  Accepted for signature parity; the
  *           result does not depend on them.
  */
-int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
+int eppgcn_spmm_forward(float *out, long long out_ld, const float *feat, long long feat_ld,
                         const int *row_ptr, const int *col_idx,
                         const float *deg_row, const float *deg_col,
                         const int *part_ptr, const int *part2node,
@@ -78,8 +83,9 @@ int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
  *   d_in[r][:] = sum over compacted edges e with ids[e] == r:
  *                (deg_row[r] * deg_col[edge_list[e]]) * d_out[edge_list[e]][:]
  *
- * d_in      [num_nodes][dim] dense fp32, fully overwritten (rows off the
- *           path come back zero).
+ * d_in      [num_nodes][dim] fp32 with a row stride of d_in_ld floats (0 =
+ *           dense), columns 0..dim-1 fully overwritten (rows off the path
+ *           come back zero).
  * ids, edge_list   outputs of eppgcn_compact_mask (valid prefix).
  * part_ptr  [num_parts+1] output of eppgcn_split_parts; part p covers
  *           compacted edges [part_ptr[p], part_ptr[p+1]) of one row.
@@ -87,7 +93,7 @@ int eppgcn_spmm_forward(float *out, const float *feat, long long feat_ld,
  *           accepted for parity; the result does not depend on them.
  * deg_col may be NULL with the same meaning as in eppgcn_spmm_forward.
  */
-int eppgcn_spmm_backward_compacted(float *d_in, const float *d_out, long long d_out_ld,
+int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *d_out, long long d_out_ld,
                                    const int *ids, const int *part_ptr, const int *edge_list,
                                    const float *deg_row, const float *deg_col,
                                    int num_nodes, int dim, int num_parts,
@@ -230,6 +236,47 @@ int eppgcn_split_parts(const int *node_deg, int num_nodes, int part_size,
 /* Number of non-zero entries, stored to *count_dev.
  * Replaces compact_count (EPPGCN/GCNConv/cuCompactor.cu:638-678, :694-696). */
 int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Row exchange between the GPUs of one node.  No counterpart in the
+ * reference, which is single-GPU: these two entry points serve the
+ * row-partitioned aggregation, where a rank's edges reference rows that
+ * other ranks own.
+ *
+ * eppgcn_push_rows gathers rows of this rank's matrix and stores them
+ * straight into other ranks' source buffers over NVLink (plain peer stores):
+ *
+ *   for r in 0..world-1, for j in [send_ptr[r], send_ptr[r+1]):
+ *     peer_base[r][(peer_first_row[r] + j - send_ptr[r]) * peer_ld + 0..dim)
+ *         = rows[send_idx[j] * rows_ld + 0..dim)
+ *
+ * rows, send_idx are device pointers of the calling GPU; send_ptr [world+1],
+ * peer_base [world] and peer_first_row [world] are HOST arrays; peer_base[r]
+ * is rank r's buffer as mapped into this process (peer access enabled, e.g.
+ * a CUDA IPC or fabric mapping), unused when rank r gets no rows.  dim,
+ * rows_ld and peer_ld are multiples of 4 floats, all bases 16-byte aligned.
+ * The caller orders the stores against the readers with eppgcn_peer_barrier.
+ *
+ * eppgcn_peer_barrier is a barrier over `world` GPUs on flag words in peer
+ * memory: peer_flags [world] (HOST array) holds every rank's array of
+ * `world` 32-bit words as mapped into this process, zero before the first
+ * barrier.  Barrier number `value` (1, 2, 3 ... the same on all ranks)
+ * stores `value` into word `rank` of every peer's array (release, system
+ * scope) and waits until all words of the own array have reached it.  Work
+ * enqueued before the barrier on any rank's stream is visible to work
+ * enqueued after it on every rank's stream.  The wait is bounded: after
+ * max_polls polls of about a microsecond each the kernel stores
+ * EPP_ERR_PEER_TIMEOUT to *status_dev (device int, set to 0 by the caller
+ * beforehand) and returns; the context stays usable.  While *status_dev is
+ * non-zero, later barriers announce their arrival but do not wait, so a
+ * broken group drains quickly; the caller reads the word and gives up.
+ */
+int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
+                     const long long *send_ptr, void *const *peer_base,
+                     const long long *peer_first_row, long long peer_ld, int dim, int world,
+                     void *stream);
+int eppgcn_peer_barrier(void *const *peer_flags, int rank, int world, unsigned value,
+                        long long max_polls, int *status_dev, void *stream);
 
 /* ------------------------------------------------------------------------
  * Measurement aid, no counterpart in the reference: performs only the gather

@@ -76,7 +76,7 @@ def test_ginfo_host_matches_oracle():
 def test_device_entry_points_validate_before_launching():
     l = capi.lib()
     # dim < 1
-    assert l.eppgcn_spmm_forward(None, None, 0, None, None, None, None, None, None, 4, 0, 0, 1, 1, 1, None) \
+    assert l.eppgcn_spmm_forward(None, 0, None, 0, None, None, None, None, None, None, 4, 0, 0, 1, 1, 1, None) \
         == capi.EPP_ERR_BAD_ARG
     assert b"dim" in l.eppgcn_last_error()
     # part size < 1

@@ -100,6 +100,46 @@ def _worker(rank, world, port, results):
         ok_halo &= bool(torch.equal(buf[mg.pos[sel].long()], want[sel]))
         ok_halo &= mg.num_rows == world * mg.cap and mg.cap == int(mask.view(world, blk).sum(1).max())
         ok_halo &= bool(torch.equal(mg.compact(torch.arange(n_eq, dtype=torch.float32))[mg.pos[sel].long()], sel.float()))
+        # --- dealt halo: remote referenced rows by all-to-all in column chunks, own rows in place ----
+        new_of_old, n_eqr = D.balanced_relabel(g.indptr, world)
+        rsh = D.make_relabelled_shard(g.indptr, g.indices, new_of_old, n_eqr, rank, world)
+        rcols = torch.from_numpy(rsh.indices)
+        dh = D.DealtHalo(rcols, n_eqr, rank, world)
+        whole = torch.arange(n_eqr * world * 24, dtype=torch.float32).reshape(n_eqr * world, 24)
+        mine = torch.zeros(n_eqr, 26)[:, :24]
+        mine.copy_(whole[rank * n_eqr:(rank + 1) * n_eqr])
+        remote = np.unique(rsh.indices[(rsh.indices // n_eqr) != rank])
+        ok_halo &= dh.num_remote == len(remote) and dh.recv_counts[rank] == 0
+        for chunks in (1, 2, 5):                              # 5 does not split 24 columns: falls back to one chunk
+            pending = dh.start(mine, chunks)
+            ok_halo &= len(pending) == (chunks if chunks < 5 else 1)
+            parts = []
+            for work, buf in pending:
+                if work is not None:
+                    work.wait()
+                parts.append(buf)
+            got = torch.cat(parts, 1)
+            ok_halo &= bool(torch.equal(got, whole[dh.order]))
+            ok_halo &= bool(torch.equal(got[dh.remap.long()], whole[rcols.long()]))
+        # --- columns mode: row block -> column slice of all rows -> row block ---------------
+        ok_cols = True
+        n_loc = -(-n // world)
+        for d in (22, 7):                                   # even and ragged split of the columns
+            ds_ = -(-d // world)
+            mat = torch.arange(n * d, dtype=torch.float32).reshape(n, d)
+            mine = torch.zeros(n_loc, d + 2)[:, :d]        # padded row stride, empty rows after the last vertex
+            rows = mat[rank * n_loc:(rank + 1) * n_loc]
+            mine[:rows.size(0)] = rows
+            send, recv = torch.zeros(world, n_loc, ds_), torch.zeros(world, n_loc, ds_)
+            src = torch.zeros(world * n_loc, ds_)
+            D.rows_to_column_slice(mine, send, src, None)
+            width = min((rank + 1) * ds_, d) - rank * ds_
+            ok_cols &= bool(torch.equal(src[:n, :width], mat[:, rank * ds_:rank * ds_ + width]))
+            ok_cols &= bool(torch.all(src[n:] == 0)) and bool(torch.all(src[:, width:] == 0))
+            back = torch.full((n_loc, d), -1.0)
+            D.column_slice_to_rows(src * 2.0, recv, back, None)
+            ok_cols &= bool(torch.equal(back, mine * 2.0))
+        ok_halo &= ok_cols
         # --- d_weight partials add up -----------------------------------------------------
         part = torch.full((4, 3), float(rank + 1))
         dist.all_reduce(part)

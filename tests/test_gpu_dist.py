@@ -1,5 +1,5 @@
-"""Row-partitioned aggregation on two real GPUs (NCCL) against the float64
-oracle of the whole graph, in all three partition/exchange modes.  Skipped on a
+"""Aggregation on two real GPUs (NCCL) against the float64 oracle of the whole
+graph: the three row-partitioned modes and the column-sliced one.  Skipped on a
 machine with fewer than two GPUs."""
 import socket
 
@@ -33,7 +33,9 @@ def _worker(rank, world, port, mode, results):
         g, n = ds.graph, ds.num_nodes
         deg = ds.degrees.numpy().copy()
         train = ds.train_mask.numpy().copy()
-        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange=mode)
+        parts = mode.split(":")                                        # "balanced_halo:2:nccl"
+        mode, chunks, transport = parts[0], (parts[1:2] or ["1"])[0], (parts[2:3] or ["push"])[0]
+        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange=mode, chunks=int(chunks), transport=transport)
         sh = hp.shard
         rng = np.random.Generator(np.random.PCG64(11))
         mats = [rng.standard_normal((n, d)).astype(np.float32) for d in (16, 22)]
@@ -57,7 +59,8 @@ def _worker(rank, world, port, mode, results):
             d = m.shape[1]
             scaled = local_rows(m * deg[:, None])                       # rows as the update step leaves them
             out = torch.empty(sh.num_rows, d, device=dev)
-            if mode == "halo":
+            dist.barrier()          # the oracle work between the steps differs per rank: line the ranks up again
+            if mode in ("halo", "balanced_halo"):
                 hp.forward_halo(scaled, out)
             else:
                 full = torch.empty(hp.n, d, device=dev)
@@ -68,6 +71,7 @@ def _worker(rank, world, port, mode, results):
             ok &= bool(err.max() <= 0)
             for i, conv in enumerate(path):
                 d_in = torch.empty(sh.num_rows, d, device=dev)
+                dist.barrier()
                 if "plan" in hp.path[i]:
                     hp.backward_halo(i, local_rows(m), d_in)
                 else:
@@ -82,13 +86,75 @@ def _worker(rank, world, port, mode, results):
         sizes = torch.tensor([p["valid"] for p in hp.path] + [p["parts"] for p in hp.path], device=dev)
         dist.all_reduce(sizes)
         ok &= sizes[:2].tolist() == [c["valid_len"] for c in path]
+        if hp.fabric is not None:
+            hp.fabric.check()                         # no bounded wait ran out
+            ok &= hp.fabric.count > 0
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+def _columns_worker(rank, world, port, results):
+    import os
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    from eppgcn_b200 import dist as D
+    from eppgcn_b200 import graphs
+    from oracle import epp_oracle as O
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=dev)
+    try:
+        ds = graphs.load_workload("pubmed", 0)          # 19,717 vertices: the last block has an empty row
+        g, n = ds.graph, ds.num_nodes
+        deg = ds.degrees.numpy().copy()
+        train = ds.train_mask.numpy().copy()
+        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange="columns")
+        v0, v1 = rank * hp.n_loc, min((rank + 1) * hp.n_loc, n)
+
+        def local_rows(m):
+            out = np.zeros((hp.n_loc, m.shape[1]), dtype=np.float32)
+            out[:v1 - v0] = m[v0:v1]
+            return torch.from_numpy(out).to(dev)
+
+        def close(got, want):
+            got, want = got.cpu().numpy()[:v1 - v0], want[v0:v1]
+            return bool((np.abs(got - want) - (2e-6 + 2e-5 * np.abs(want))).max() <= 0)
+
+        path, _ = O.prepare_execution_path(g.indptr, g.indices, train, 2, hp.part_size, [8, 8])
+        ok = [p["valid"] for p in hp.path] == [c["valid_len"] for c in path]
+        ok &= [p["parts"] for p in hp.path] == [c["numParts"] for c in path]
+        rng = np.random.Generator(np.random.PCG64(11))
+        key = 0
+        for d in (16, 22, 7):                             # 7 columns over 2 ranks: ragged last block
+            m = rng.standard_normal((n, d)).astype(np.float32)
+            out = torch.empty(hp.n_loc, d, device=dev)
+            hp.columns_op(key, "fwd", 0, local_rows(m * deg[:, None]), out)
+            key += 1
+            ok &= close(out, O.spmm_forward(g.indptr, g.indices, deg, m))
+            for i, conv in enumerate(path):
+                d_in = torch.empty(hp.n_loc, d, device=dev)
+                hp.columns_op(key, "bwd", i, local_rows(m), d_in)
+                key += 1
+                ok &= close(d_in, O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg,
+                                                            m, conv["numParts"]))
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo"])
+def test_two_gpus_column_slices_match_the_whole_graph_oracle():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_columns_worker, args=(2, _free_port(), results), nprocs=2, join=True)
+    assert dict(results) == {0: True, 1: True}
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2", "balanced_halo:2:nccl"])
 def test_two_gpus_match_the_whole_graph_oracle(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

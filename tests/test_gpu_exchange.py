@@ -1,0 +1,60 @@
+"""The two exchange kernels on one GPU: the row push with local buffers
+standing in for the peers' ones, and the flag barrier including its bounded
+wait (a flag that nobody sets makes it run out; the context stays usable)."""
+import numpy as np
+import pytest
+import torch
+
+from eppgcn_b200 import capi
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("dim,pad", [(4, 0), (16, 0), (32, 8), (64, 0)])
+def test_push_rows_places_every_row(cuda, dim, pad):
+    rng = np.random.Generator(np.random.PCG64(dim))
+    n, world = 5000, 3
+    rows = torch.randn(n, dim + pad, device=cuda)[:, :dim]
+    counts = [700, 0, 1300]                                   # the middle "rank" gets nothing
+    idx = torch.from_numpy(rng.integers(0, n, sum(counts)).astype(np.int32)).to(cuda)
+    send_ptr = [0] + np.cumsum(counts).tolist()
+    first = [11, 0, 5]
+    bufs = [torch.full((c + first[r] + 3, dim), -1.0, device=cuda) for r, c in enumerate(counts)]
+    capi.push_rows(rows, idx, send_ptr, [b.data_ptr() for b in bufs], first, dim)
+    torch.cuda.synchronize()
+    for r, c in enumerate(counts):
+        got = bufs[r]
+        want = rows[idx[send_ptr[r]:send_ptr[r + 1]].long()]
+        assert torch.equal(got[first[r]:first[r] + c], want)
+        assert bool((got[:first[r]] == -1).all()) and bool((got[first[r] + c:] == -1).all())
+
+
+def test_push_rows_rejects_ragged_rows(cuda):
+    rows = torch.randn(8, 6, device=cuda)
+    idx = torch.zeros(1, dtype=torch.int32, device=cuda)
+    with pytest.raises(capi.EppError) as e:
+        capi.push_rows(rows, idx, [0, 1], [rows.data_ptr()], [0], 6)
+    assert e.value.status == capi.EPP_ERR_BAD_ARG
+
+
+def test_barrier_passes_alone_and_reports_a_missing_peer(cuda):
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    mine = torch.zeros(64, dtype=torch.int32, device=cuda)
+    other = torch.zeros(64, dtype=torch.int32, device=cuda)
+    # a group of one: the rank's own word is all it waits for
+    for value in (1, 2, 3):
+        capi.peer_barrier([mine.data_ptr()], 0, value, status)
+    torch.cuda.synchronize()
+    assert status.item() == capi.EPP_OK and mine[0].item() == 3
+    # two ranks, the other one never arrives: its word stays 0, the wait runs out
+    mine.zero_()
+    capi.peer_barrier([mine.data_ptr(), other.data_ptr()], 0, 1, status, max_polls=2000)
+    torch.cuda.synchronize()
+    assert status.item() == capi.EPP_ERR_PEER_TIMEOUT
+    assert other[0].item() == 1                   # the arrival was announced before the wait
+    # the other rank "arrives": the same barrier now passes
+    status.zero_()
+    mine[1] = 1
+    capi.peer_barrier([mine.data_ptr(), other.data_ptr()], 0, 1, status, max_polls=2000)
+    torch.cuda.synchronize()
+    assert status.item() == capi.EPP_OK

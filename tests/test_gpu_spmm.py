@@ -219,3 +219,33 @@ def test_operator_backward_products_match_float64(cuda):
         assert_close(d_in.cpu().numpy(), wi, 2e-5, 2e-6, f"d_input {din}->{dout}")
         s = float(np.abs(ww).max())
         assert_close(d_w.cpu().numpy() / s, ww / s, 1e-4, 1e-5, f"d_weight {din}->{dout}")
+
+
+@pytest.mark.parametrize("dim,left,right", [(8, 8, 0), (8, 4, 4), (22, 2, 0), (5, 3, 1), (64, 64, 64)])
+def test_results_land_in_a_column_block_of_a_wider_matrix(cuda, dim, left, right):
+    """Output rows with a stride: forward and compacted backward fill columns
+    left .. left+dim of a wider matrix and leave the columns on either side alone."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    rng = np.random.Generator(np.random.PCG64(5))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    deg = degrees_of(indptr, "rsqrt")
+    pp, p2n = O.build_part(6, indptr)
+    wide = torch.full((n, left + dim + right), 7.0, device=cuda)
+    capi.spmm_forward(t(feat, cuda), t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda), t(p2n, cuda), 6,
+                      out=wide[:, left:left + dim])
+    got = wide.cpu().numpy()
+    assert_close(got[:, left:left + dim], O.spmm_forward(indptr, indices, deg, feat), what="forward column block")
+    assert (got[:, :left] == 7.0).all() and (got[:, left + dim:] == 7.0).all()
+
+    train = rng.random(n) < 0.2
+    path, _ = O.prepare_execution_path(indptr, indices, train, 1, 6, [8])
+    conv = path[0]
+    wide.fill_(7.0)
+    capi.spmm_backward_compacted(t(feat, cuda), t(conv["id"], cuda), t(conv["partPointer"], cuda),
+                                 t(conv["edgeList"], cuda), t(deg, cuda), conv["numParts"], 8,
+                                 out=wide[:, left:left + dim])
+    got = wide.cpu().numpy()
+    want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, feat, conv["numParts"])
+    assert_close(got[:, left:left + dim], want, what="backward column block")
+    assert (got[:, :left] == 7.0).all() and (got[:, left + dim:] == 7.0).all()

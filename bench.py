@@ -429,7 +429,7 @@ def main():
     p.add_argument("--workload", default="rmat21")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--backsize", type=int, default=32)
-    p.add_argument("--exchange", default="balanced", choices=["balanced", "allgather", "halo", "balanced_halo", "columns"],
+    p.add_argument("--exchange", default="balanced", choices=["balanced", "allgather", "halo", "balanced_halo"],
                    help="multi-GPU partition/exchange, see eppgcn_b200.dist.DistHotPath")
     p.add_argument("--chunks", type=int, default=1,
                    help="balanced_halo: column chunks per exchange (aggregation of one overlaps the transfer of the next)")

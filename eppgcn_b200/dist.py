@@ -1,7 +1,7 @@
 """Row-partitioned data parallelism for the GCN aggregation hot path.
 
 The reference is single-GPU.  Destination rows are independent once the whole
-source matrix is visible, so every rank owns a set of destination rows.  Three
+source matrix is visible, so every rank owns a set of destination rows.  Four
 ways of choosing and exchanging them are kept, selected by ``exchange``:
 
   ``balanced``   (default) vertices are relabelled by a degree-sorted round robin,
@@ -12,17 +12,16 @@ ways of choosing and exchanging them are kept, selected by ``exchange``:
   ``allgather``  contiguous vertex ranges with (nearly) equal edge counts; blocks
                  are uneven, so the exchange pads to the largest one.
   ``halo``       contiguous ranges, but only the rows a rank's edges touch travel
-                 (``HaloPlan``, all-to-all); least traffic, slowest in practice.
-  ``columns``    every rank keeps the whole graph and aggregates ``D / world``
-                 feature columns of every row: an all-to-all turns the rank's row
-                 block of the source matrix into its column slice of all rows, the
-                 SpMM runs over the full edge list on that slice, and a second
-                 all-to-all turns the result back into row blocks.  A rank sends
-                 and receives ``2 N D / world`` floats per aggregation instead of
-                 the ``N D (world - 1) / world`` of a row all-gather, and no rank
-                 depends on how the edges are spread over the rows.
+                 (``HaloPlan``, all-to-all); slowest in practice (uneven pairs).
+  ``balanced_halo``  the relabelling of ``balanced`` with a halo exchange
+                 (``DealtHalo``): only the remote rows a rank's edges reference
+                 travel, the rank's own rows never move, and the transfer is one
+                 kernel of this package that gathers the rows and stores them
+                 straight into the readers' buffers over NVLink, ordered by a flag
+                 barrier with bounded waits (``PeerFabric``); NCCL all-to-all is the
+                 alternative transport.
 
-Per layer, in the row-partitioned modes:
+Per layer (``all-gather`` stands for whichever exchange the mode uses):
 
   forward, per layer    local ``X_g @ W`` -> all-gather of the (narrow) post-update
                         rows into every rank's own memory -> local SpMM over the
@@ -34,8 +33,9 @@ Per layer, in the row-partitioned modes:
                         over the rank's own parts -> local ``d_input`` rows;
                         ``d_weight`` partials are all-reduced.
 
-Remote rows always land in local memory first (NCCL over NVLink); kernels never
-read a peer's memory.  The host-side logic (ranges, shards, row exchange, mask
+Remote rows always land in the reader's own memory before any kernel reads them
+(NCCL, or peer stores by the owner); no kernel loads from a peer's memory.  The
+host-side logic (ranges, shards, row exchange, mask
 reduction) runs unchanged on the ``gloo`` backend and is tested there.
 """
 from __future__ import annotations
@@ -204,38 +204,6 @@ def _padded_rows(t: torch.Tensor) -> torch.Tensor:
         raise ValueError("expected a 2-D tensor with unit column stride")
     ld = t.stride(0) if t.size(0) > 1 else max(t.stride(0), t.size(1))
     return t if ld == t.size(1) else torch.as_strided(t, (t.size(0), ld), (ld, 1), t.storage_offset())
-
-
-def rows_to_column_slice(local: torch.Tensor, send: torch.Tensor, src: torch.Tensor, group=None):
-    """This rank's row block ``local [n_loc, d]`` of a matrix -> its column slice
-    ``src [world * n_loc, ceil(d / world)]`` of all rows.  ``send [world, n_loc,
-    ceil(d / world)]`` stages the block-major copy: block ``b`` holds the columns
-    rank ``b`` owns and is what rank ``b`` receives as its rows ``rank * n_loc ..``.
-    With a ragged last block the padding columns of ``send`` must be zero."""
-    w, ds_, d = send.size(0), send.size(2), local.size(1)
-    if d == w * ds_:
-        send.copy_(local.unflatten(1, (w, ds_)).transpose(0, 1))
-    else:
-        for b in range(-(-d // ds_)):
-            hi = min((b + 1) * ds_, d)
-            send[b, :, :hi - b * ds_].copy_(local[:, b * ds_:hi])
-    dist.all_to_all_single(src.view(-1), send.view(-1), group=group)
-    return src
-
-
-def column_slice_to_rows(agg: torch.Tensor, recv: torch.Tensor, local: torch.Tensor, group=None):
-    """Inverse of :func:`rows_to_column_slice`: ``agg [world * n_loc, ds]`` (this
-    rank's columns of all rows; rank ``b``'s rows are one contiguous block, so it
-    is the send buffer as it stands) -> ``local [n_loc, d]``."""
-    w, ds_, d = recv.size(0), recv.size(2), local.size(1)
-    dist.all_to_all_single(recv.view(-1), agg.view(-1), group=group)
-    if d == w * ds_:
-        local.unflatten(1, (w, ds_)).copy_(recv.transpose(0, 1))
-    else:
-        for b in range(-(-d // ds_)):
-            hi = min((b + 1) * ds_, d)
-            local[:, b * ds_:hi].copy_(recv[b, :, :hi - b * ds_])
-    return local
 
 
 class HaloPlan:
@@ -501,8 +469,6 @@ class DistHotPath:
     ``"balanced_halo"``  the relabelling of ``balanced`` with the exchange of
                      ``halo``: the dealt-out rows make the per-pair row counts of
                      the all-to-all nearly equal, and only referenced rows travel.
-    ``"columns"``    whole graph on every rank, ``ceil(D / world)`` feature columns
-                     each; two equal-split all-to-alls per aggregation.
     """
 
     def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None,
@@ -513,14 +479,11 @@ class DistHotPath:
         self.mode, self.chunks, self.fabric = exchange, chunks, None
         gnna = eppgcn_b200.load_gnnadvisor()
         on_device = torch.is_tensor(getattr(ds, "indptr", None))      # DeviceWorkload: the graph never touches the host
-        if exchange == "columns":
-            self._init_columns(ds, gnna, on_device, back_size)
-            return
         relabel = exchange in ("balanced", "balanced_halo")
         halo = exchange in ("halo", "balanced_halo")
         if on_device:
             if not relabel:
-                raise ValueError("device-resident workloads support the balanced, balanced_halo and columns modes")
+                raise ValueError("device-resident workloads support the balanced and balanced_halo modes")
             new_of_old, n_loc, local_ptr, cols = balanced_shard_device(ds.indptr, ds.indices, rank, world)
             self.new_of_old = new_of_old
             self.n = n_loc * world
@@ -626,89 +589,6 @@ class DistHotPath:
             torch.cuda.synchronize(dev)
             self.plan_s = time.perf_counter() - t0
 
-    def _init_columns(self, ds, gnna, on_device, back_size):
-        """Whole graph on this rank; the execution path is prepared locally, with
-        no mask exchange, exactly as on one GPU."""
-        capi, dev, world = self.capi, self.dev, self.world
-        if on_device:
-            indptr, col = ds.indptr.to(torch.int32), ds.indices
-            deg, train = ds.degrees.to(dev), ds.train_mask.to(dev)
-        else:
-            g = ds.graph
-            indptr = torch.from_numpy(g.indptr).to(dev, torch.int32)
-            col = torch.from_numpy(g.indices).to(dev, torch.int32)
-            deg, train = ds.degrees.to(dev), ds.train_mask.to(dev)
-        n = indptr.numel() - 1
-        n_loc = -(-n // world)
-        n_pad = n_loc * world
-        if n_pad > n:                               # empty rows fill the last rank's block
-            indptr = torch.cat([indptr, indptr[-1:].expand(n_pad - n)])
-            deg = torch.cat([deg, torch.ones(n_pad - n, device=dev)])
-            train = torch.cat([train, torch.zeros(n_pad - n, dtype=torch.bool, device=dev)])
-        self.n, self.n_loc, self.new_of_old = n_pad, n_loc, None
-        self.bounds = np.arange(world + 1, dtype=np.int64) * n_loc
-        self.part_size = max(int(ds.avg_degree), 1)
-        row_cpu = indptr.cpu()
-        self.shard = RowShard(self.rank, 0, n_pad, row_cpu, col)
-        pp, p2n = gnna.build_part(self.part_size, row_cpu)
-        self.row, self.col, self.pp, self.p2n = indptr.contiguous(), col, pp.to(dev), p2n.to(dev)
-        self.deg = self.deg_row = deg.contiguous()
-        L, e = ds.num_layers, col.numel()
-        ngh = [torch.zeros(n_pad, dtype=torch.bool, device=dev) for _ in range(L - 1)]
-        node_degs = [torch.zeros(n_pad, dtype=torch.int32, device=dev) for _ in range(L)]
-        torch.cuda.synchronize(dev)
-        t0 = time.perf_counter()
-        self.path = [None] * L
-        for i in range(L):
-            j = L - 1 - i
-            edge_mask = torch.full((e,), -1, dtype=torch.int32, device=dev)
-            capi.mask_forward(self.p2n, self.pp, self.col, train if i == 0 else ngh[i - 1],
-                              ngh[i] if i < L - 1 else None, edge_mask, node_degs[j], L, i + 1)
-            ids, edges, valid = capi.compact_mask(edge_mask, self.col)
-            del edge_mask
-            ids, edges = ids[:valid].clone(), edges[:valid].clone()      # keep only the marked part resident
-            ppb, parts = capi.split_parts(node_degs[j], e, back_size)
-            self.path[j] = dict(id=ids, edges=edges, pp=ppb[:parts + 1].clone(), parts=parts, valid=valid,
-                                rows=int(torch.count_nonzero(node_degs[j]).item()))
-        torch.cuda.synchronize(dev)
-        self.prep_s = time.perf_counter() - t0
-        self.ngh_masks, self.node_degs, self.back_size = ngh, node_degs, back_size
-        self._cols = {}
-
-    def col_slice(self, d: int) -> int:
-        """Feature columns per rank for a ``d``-wide matrix."""
-        return -(-d // self.world)
-
-    def _column_buffers(self, key, d):
-        """Per-aggregation buffers: block-major send rows, the column slice of all
-        rows before and after the SpMM, block-major received rows."""
-        if key not in self._cols:
-            w, ds_ = self.world, self.col_slice(d)
-            mk = lambda *shape: torch.zeros(*shape, device=self.dev)
-            self._cols[key] = dict(send=mk(w, self.n_loc, ds_), src=mk(self.n, ds_), agg=mk(self.n, ds_),
-                                   recv=mk(w, self.n_loc, ds_))
-        return self._cols[key]
-
-    def columns_local(self, key, kind, i, d):
-        """The SpMM of one aggregation on this rank's column slice of all rows."""
-        b = self._column_buffers(key, d)
-        if kind == "fwd":
-            return self.capi.spmm_forward(b["src"], self.row, self.col, self.deg, self.pp, self.p2n, self.part_size,
-                                          out=b["agg"], prescaled=True)
-        p = self.path[i]
-        return self.capi.spmm_backward_compacted(b["src"], p["id"], p["pp"], p["edges"], self.deg, p["parts"],
-                                                 self.back_size, out=b["agg"], num_rows=self.n)
-
-    def columns_op(self, key, kind, i, local_in, out_local):
-        """One aggregation in the ``columns`` mode: row block -> column slice
-        (all-to-all), SpMM over the whole graph, column slice -> row block."""
-        d = local_in.size(1)
-        b = self._column_buffers(key, d)
-        rows_to_column_slice(local_in, b["send"], b["src"], self.group)
-        self.columns_local(key, kind, i, d)
-        column_slice_to_rows(b["agg"], b["recv"], out_local, self.group)
-        return out_local
-
     def gather(self, full, local):
         return all_gather_rows(full, local, self.bounds, self.group)
 
@@ -804,9 +684,9 @@ def run_bench(args, rank: int, world: int, dev):
     n, e, L = ds.num_nodes, ds.num_edges, ds.num_layers
     dims = [spec["hidden"]] * (L - 1) + [spec["classes"]]
     mode = getattr(args, "exchange", "balanced")
-    if device_drawn and mode not in ("balanced", "balanced_halo", "columns"):
+    if device_drawn and mode not in ("balanced", "balanced_halo"):
         mode = "balanced"
-    halo, columns = mode in ("halo", "balanced_halo"), mode == "columns"
+    halo = mode in ("halo", "balanced_halo")
     hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=getattr(args, "chunks", 1),
                      transport=getattr(args, "transport", "push"))
     dealt = mode == "balanced_halo"
@@ -835,8 +715,8 @@ def run_bench(args, rank: int, world: int, dev):
     full = [None] * len(ops)
     bufs = [None] * len(ops)
     for k, (kind, i, d) in enumerate(ops):
-        if columns or dealt:
-            continue                                  # these modes keep their own per-aggregation buffers
+        if dealt:
+            continue                                  # the plans keep their own per-aggregation buffers
         if halo:
             bufs[k] = (hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).exchange(local_in[k])
         elif kind == "bwd" and compact_bwd:
@@ -846,9 +726,7 @@ def run_bench(args, rank: int, world: int, dev):
 
     def one(k):
         kind, i, d = ops[k]
-        if columns:
-            hp.columns_op(k, kind, i, local_in[k], outs[k])
-        elif kind == "bwd" and compact_bwd:
+        if kind == "bwd" and compact_bwd:
             hp.backward_halo(i, local_in[k], outs[k])
         elif halo:
             hp.forward_halo(local_in[k], outs[k])
@@ -858,8 +736,6 @@ def run_bench(args, rank: int, world: int, dev):
 
     def local_only(k):
         kind, i, d = ops[k]
-        if columns:
-            return hp.columns_local(k, kind, i, d)
         if dealt:
             return hp.halo_local(kind, i, outs[k])
         if kind == "fwd":
@@ -958,16 +834,12 @@ def run_bench(args, rank: int, world: int, dev):
                                                  "rows per aggregation",
                                          "allgather": "contiguous ranges, one uneven NCCL row all-gather per aggregation",
                                          "balanced_halo": "degree-dealt relabelling (equal rows and edges per "
-                                                          "rank), NCCL all-to-all of the referenced remote source "
-                                                          f"rows in {hp.chunks} column chunk(s) per aggregation, "
+                                                          "rank); per aggregation only the referenced remote source "
+                                                          f"rows travel, in {hp.chunks} column chunk(s), "
                                                           + ("gathered and stored into the readers' buffers over "
                                                              "NVLink by one kernel of this library, flag barriers "
                                                              "with bounded waits" if hp.fabric is not None else
-                                                             "NCCL all-to-all"),
-                                         "columns": "whole graph on every rank, ceil(D/world) feature columns each; "
-                                                    "two equal-split NCCL all-to-alls per aggregation (row block "
-                                                    "-> column slice -> row block), layout copies inside the timed "
-                                                    "region",
+                                                             "by NCCL all-to-all"),
                                          "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
                                                      "NCCL all-gather per aggregation (source-mask rows only for "
                                                      "the backward layers)"}[mode]},

@@ -121,25 +121,6 @@ def _worker(rank, world, port, results):
             got = torch.cat(parts, 1)
             ok_halo &= bool(torch.equal(got, whole[dh.order]))
             ok_halo &= bool(torch.equal(got[dh.remap.long()], whole[rcols.long()]))
-        # --- columns mode: row block -> column slice of all rows -> row block ---------------
-        ok_cols = True
-        n_loc = -(-n // world)
-        for d in (22, 7):                                   # even and ragged split of the columns
-            ds_ = -(-d // world)
-            mat = torch.arange(n * d, dtype=torch.float32).reshape(n, d)
-            mine = torch.zeros(n_loc, d + 2)[:, :d]        # padded row stride, empty rows after the last vertex
-            rows = mat[rank * n_loc:(rank + 1) * n_loc]
-            mine[:rows.size(0)] = rows
-            send, recv = torch.zeros(world, n_loc, ds_), torch.zeros(world, n_loc, ds_)
-            src = torch.zeros(world * n_loc, ds_)
-            D.rows_to_column_slice(mine, send, src, None)
-            width = min((rank + 1) * ds_, d) - rank * ds_
-            ok_cols &= bool(torch.equal(src[:n, :width], mat[:, rank * ds_:rank * ds_ + width]))
-            ok_cols &= bool(torch.all(src[n:] == 0)) and bool(torch.all(src[:, width:] == 0))
-            back = torch.full((n_loc, d), -1.0)
-            D.column_slice_to_rows(src * 2.0, recv, back, None)
-            ok_cols &= bool(torch.equal(back, mine * 2.0))
-        ok_halo &= ok_cols
         # --- d_weight partials add up -----------------------------------------------------
         part = torch.full((4, 3), float(rank + 1))
         dist.all_reduce(part)

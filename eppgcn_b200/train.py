@@ -169,8 +169,13 @@ class GCNTrainer:
 
 
 def main(argv=None):
-    p = argparse.ArgumentParser(description="GCN training on a seeded synthetic workload")
-    p.add_argument("--dataset", default="pubmed", choices=sorted(WORKLOADS))
+    p = argparse.ArgumentParser(description="GCN training on a seeded synthetic workload, or on the reference's "
+                                            "graph files when --dataDir is given")
+    p.add_argument("--dataDir", default=None,
+                   help="folder with <dataset>_snap or <dataset>.npz and train_mask_<ratio> (EPPGCN/gcn_main.py:21,73-78)")
+    p.add_argument("--loadFromTxt", default="True", choices=["True", "False"])
+    p.add_argument("--dataset", default="pubmed",
+                   help="a synthetic workload (" + ", ".join(sorted(WORKLOADS)) + ") or, with --dataDir, a file stem")
     p.add_argument("--dim", type=int, default=None)
     p.add_argument("--hidden", type=int, default=None)
     p.add_argument("--classes", type=int, default=None)
@@ -187,11 +192,22 @@ def main(argv=None):
     a = p.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA device is required (there is no CPU fallback)")
-    spec = WORKLOADS[a.dataset]
-    ds = load_workload(a.dataset, a.seed, train_ratio=a.train_ratio, layers=a.layers)
-    if a.dim is not None or a.classes is not None:
-        raise SystemExit("--dim/--classes are fixed by the workload in this harness")
-    print("||{}   {}   {}".format(a.dataset, a.train_ratio or spec["train_ratio"], ds.num_layers))
+    if a.dataDir is not None:
+        # the reference's defaults (EPPGCN/gcn_main.py:23-27)
+        spec = dict(hidden=16, train_ratio=0.1)
+        from .loader import load_dataset_files
+        ds = load_dataset_files(a.dataDir, a.dataset, a.train_ratio if a.train_ratio is not None else 0.1,
+                                a.dim or 96, a.classes or 22, a.layers or 2,
+                                load_from_txt=a.loadFromTxt == "True", seed=a.seed)
+    else:
+        if a.dataset not in WORKLOADS:
+            raise SystemExit(f"unknown workload {a.dataset!r}; give --dataDir to read graph files")
+        spec = WORKLOADS[a.dataset]
+        ds = load_workload(a.dataset, a.seed, train_ratio=a.train_ratio, layers=a.layers)
+        if a.dim is not None or a.classes is not None:
+            raise SystemExit("--dim/--classes are fixed by the synthetic workloads")
+    ratio = a.train_ratio if a.train_ratio is not None else spec["train_ratio"]
+    print("||{}   {}   {}".format(a.dataset, ratio, ds.num_layers))
     tr = GCNTrainer(ds, hidden=a.hidden or spec["hidden"], backsize_mode=a.backsize_mode, backsize=a.backsize,
                     partSize=a.partSize, dimWorker=a.dimWorker, warpPerBlock=a.warpPerBlock,
                     sharedMem=a.sharedMem, prepare_before_training=False, seed=a.seed)

@@ -429,10 +429,11 @@ def main():
     p.add_argument("--workload", default="rmat21")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--backsize", type=int, default=32)
-    p.add_argument("--exchange", default="balanced", choices=["balanced", "allgather", "halo", "balanced_halo"],
+    p.add_argument("--exchange", default="balanced_halo", choices=["balanced", "allgather", "halo", "balanced_halo"],
                    help="multi-GPU partition/exchange, see eppgcn_b200.dist.DistHotPath")
-    p.add_argument("--chunks", type=int, default=1,
-                   help="balanced_halo: column chunks per exchange (aggregation of one overlaps the transfer of the next)")
+    p.add_argument("--chunks", type=int, default=0,
+                   help="balanced_halo: column chunks per exchange, one compact source buffer each; 0 = two when "
+                        "every layer is at least 32 columns wide (and splits into 16-byte pieces), else one")
     p.add_argument("--transport", default="push", choices=["push", "nccl"],
                    help="balanced_halo: peer stores by this library's kernel, or NCCL all-to-all")
     p.add_argument("--no-cpu-baseline", action="store_true")

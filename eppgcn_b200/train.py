@@ -61,7 +61,7 @@ class GCNTrainer:
 
     def __init__(self, dataset, hidden=16, backsize_mode="constant", backsize=32,
                  partSize=32, dimWorker=32, warpPerBlock=8, sharedMem=100,
-                 prepare_before_training=True, seed=0, device="cuda"):
+                 prepare_before_training=True, seed=0, device="cuda", manual_mode=False, verbose=False):
         self.ds = dataset
         self.device = torch.device(device)
         self.layers = dataset.num_layers
@@ -72,7 +72,8 @@ class GCNTrainer:
         ds.to(self.device)      # degrees, features and masks live on the GPU; the CSR stays on the host for build_part
 
         info = inputProperty(ds.row_pointers, ds.column_index, ds.degrees, partSize, dimWorker, warpPerBlock,
-                             sharedMem, hiddenDim=hidden, dataset_obj=ds, manual_mode=False)
+                             sharedMem, hiddenDim=hidden, dataset_obj=ds, manual_mode=manual_mode,
+                             verbose=verbose)
         info.decider()
         t0 = time.perf_counter()
         partPtr, part2Node = GNNA.build_part(info.partSize, ds.row_pointers.cpu())
@@ -168,7 +169,9 @@ class GCNTrainer:
         return loss
 
 
-def main(argv=None):
+def build_parser() -> argparse.ArgumentParser:
+    """The flags of the reference's training script (EPPGCN/gcn_main.py:19-52),
+    so that its sweep script's command lines parse unchanged."""
     p = argparse.ArgumentParser(description="GCN training on a seeded synthetic workload, or on the reference's "
                                             "graph files when --dataDir is given")
     p.add_argument("--dataDir", default=None,
@@ -187,9 +190,23 @@ def main(argv=None):
     p.add_argument("--warpPerBlock", type=int, default=8)
     p.add_argument("--sharedMem", type=int, default=100)
     p.add_argument("--backsize", type=int, default=32)
-    p.add_argument("--backsize_mode", default="constant", choices=["map", "bucket", "constant"])
+    p.add_argument("--backsize_mode", default="constant", choices=["map", "net", "bucket", "constant"])
     p.add_argument("--seed", type=int, default=0)
-    a = p.parse_args(argv)
+    p.add_argument("--model", default="gcn", choices=["gcn", "gin"])
+    for flag in ("--manual_mode", "--verbose_mode", "--single_spmm", "--verify_spmm"):
+        p.add_argument(flag, default="False", choices=["True", "False"])
+    return p
+
+
+def main(argv=None):
+    a = build_parser().parse_args(argv)
+    if a.model != "gcn":
+        raise SystemExit("only the GCN path is built (the GIN layers of the reference's script are commented out)")
+    if a.backsize_mode == "net":
+        raise SystemExit("--backsize_mode net needs the reference's trained PyG part-size predictor, which is not "
+                         "part of it; use map, bucket or constant")
+    if a.single_spmm == "True" or a.verify_spmm == "True":
+        raise SystemExit("--single_spmm / --verify_spmm: use bench.py --kernels-only and the parity tests instead")
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA device is required (there is no CPU fallback)")
     if a.dataDir is not None:
@@ -210,7 +227,8 @@ def main(argv=None):
     print("||{}   {}   {}".format(a.dataset, ratio, ds.num_layers))
     tr = GCNTrainer(ds, hidden=a.hidden or spec["hidden"], backsize_mode=a.backsize_mode, backsize=a.backsize,
                     partSize=a.partSize, dimWorker=a.dimWorker, warpPerBlock=a.warpPerBlock,
-                    sharedMem=a.sharedMem, prepare_before_training=False, seed=a.seed)
+                    sharedMem=a.sharedMem, prepare_before_training=False, seed=a.seed,
+                    manual_mode=a.manual_mode == "True", verbose=a.verbose_mode == "True")
     for i in range(10):                       # dry run, EPPGCN/gcn_main.py:272-273
         tr.train_epoch(i == 0, timed=True)
     tr.for_time = tr.loss_time = tr.back_time = 0.0

@@ -407,7 +407,7 @@ class DealtHalo:
                 buf[self.num_remote:].copy_(local[:, c * dc:(c + 1) * dc])
             part = buf[self.num_remote:]
             work = None
-            if self.world > 1 and self.num_remote + send.size(0) > 0:
+            if self.world > 1:                   # every rank joins, also one that neither sends nor receives
                 torch.index_select(part, 0, self.send_idx, out=send)
                 work = dist.all_to_all_single(buf[:self.num_remote], send, self.recv_counts, self.send_counts,
                                               group=self.group, async_op=True)

@@ -121,6 +121,14 @@ def _worker(rank, world, port, results):
             got = torch.cat(parts, 1)
             ok_halo &= bool(torch.equal(got, whole[dh.order]))
             ok_halo &= bool(torch.equal(got[dh.remap.long()], whole[rcols.long()]))
+        # a rank whose edges reference nothing (empty path), and one that references only its own rows
+        lonely = D.DealtHalo(torch.zeros(0, dtype=torch.int32) if rank == 0 else
+                             torch.arange(rank * n_eqr, rank * n_eqr + 5, dtype=torch.int32), n_eqr, rank, world)
+        ok_halo &= lonely.num_remote == 0 and lonely.num_rows == n_eqr and sum(lonely.send_counts) == 0
+        (work, buf), = lonely.start(mine, 1)
+        if work is not None:
+            work.wait()
+        ok_halo &= bool(torch.equal(buf, mine)) and (rank == 0 or lonely.remap.tolist() == list(range(5)))
         # --- d_weight partials add up -----------------------------------------------------
         part = torch.full((4, 3), float(rank + 1))
         dist.all_reduce(part)

@@ -61,7 +61,8 @@ class GCNTrainer:
 
     def __init__(self, dataset, hidden=16, backsize_mode="constant", backsize=32,
                  partSize=32, dimWorker=32, warpPerBlock=8, sharedMem=100,
-                 prepare_before_training=True, seed=0, device="cuda", manual_mode=False, verbose=False):
+                 prepare_before_training=True, seed=0, device="cuda", manual_mode=False, verbose=False,
+                 path_cache_dir=None):
         self.ds = dataset
         self.device = torch.device(device)
         self.layers = dataset.num_layers
@@ -97,9 +98,23 @@ class GCNTrainer:
         torch.manual_seed(seed)
         self.model = Net(L, ds.num_features, hidden, ds.num_classes).to(self.device)
         self.optimizer = torch.optim.Adam(self.model.parameters(), lr=0.01)
-        self.prepared = False
+        self.prepared = self.path_from_cache = False
         self.is_net_order = prepare_before_training
-        if prepare_before_training:
+        self.path_cache_dir, self._path_fp = path_cache_dir, None
+        if path_cache_dir:
+            # a path prepared by an earlier run for the same graph, mask and knobs is read back instead
+            from . import path_cache
+            t0 = time.perf_counter()
+            self._path_fp = path_cache.fingerprint(ds.row_pointers, ds.column_index, ds.train_mask, L, info.partSize,
+                                                   backsize_mode, backsize)
+            cached = path_cache.load(path_cache_dir, self._path_fp, self.device)
+            if cached is not None and len(cached) == L:
+                for prop, c in zip(self.back_props, cached):
+                    prop.fillProperty(c["id"], c["partPointer"], c["edgeList"], c["partSize"], c["numParts"])
+                    prop.valid_len = c["valid_len"]
+                self.prepared = self.path_from_cache = True
+                self.build_time += time.perf_counter() - t0
+        if prepare_before_training and not self.prepared:
             t0 = time.perf_counter()
             for i in range(L):
                 self.mask_forward(i)
@@ -136,6 +151,9 @@ class GCNTrainer:
             self.back_props[i].fillProperty(ids, part_pointer, edge_list, ps, int(nparts[0].item()))
             self.back_props[i].valid_len = valid_len
         self.prepared = True
+        if self.path_cache_dir:
+            from . import path_cache
+            path_cache.save(self.path_cache_dir, self._path_fp, self.back_props)
 
     def forward(self, x=None, isFirstIter=False):
         return self.model(self.ds.x if x is None else x, self.inputInfo, self.mask_props, self.back_props,
@@ -143,6 +161,8 @@ class GCNTrainer:
 
     # EPPGCN/gcn_main.py:225-265
     def train_epoch(self, isFirstIter=False, timed=False, x=None):
+        if self.path_from_cache:
+            isFirstIter = False                      # nothing to mark or to build: the path came from disk
         self.model.train()
         self.optimizer.zero_grad()
         t0 = time.perf_counter()
@@ -192,6 +212,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--backsize", type=int, default=32)
     p.add_argument("--backsize_mode", default="constant", choices=["map", "net", "bucket", "constant"])
     p.add_argument("--seed", type=int, default=0)
+    p.add_argument("--path_cache", default=None,
+                   help="folder for prepared execution paths; a matching one is loaded instead of prepared again")
     p.add_argument("--model", default="gcn", choices=["gcn", "gin"])
     for flag in ("--manual_mode", "--verbose_mode", "--single_spmm", "--verify_spmm"):
         p.add_argument(flag, default="False", choices=["True", "False"])
@@ -228,7 +250,8 @@ def main(argv=None):
     tr = GCNTrainer(ds, hidden=a.hidden or spec["hidden"], backsize_mode=a.backsize_mode, backsize=a.backsize,
                     partSize=a.partSize, dimWorker=a.dimWorker, warpPerBlock=a.warpPerBlock,
                     sharedMem=a.sharedMem, prepare_before_training=False, seed=a.seed,
-                    manual_mode=a.manual_mode == "True", verbose=a.verbose_mode == "True")
+                    manual_mode=a.manual_mode == "True", verbose=a.verbose_mode == "True",
+                    path_cache_dir=a.path_cache)
     for i in range(10):                       # dry run, EPPGCN/gcn_main.py:272-273
         tr.train_epoch(i == 0, timed=True)
     tr.for_time = tr.loss_time = tr.back_time = 0.0

@@ -11,7 +11,9 @@ operators need a GPU and are used by the GPU parity tests as the reference
 side.  The reference's own ``setup.py`` passes no architecture flag
 (EPPGCN/GCNConv/setup.py:15-16); sm_100 is selected here.
 
-Usage: ``python oracle/build_ref.py [reference_root]`` (default /root/reference).
+Usage: ``python oracle/build_ref.py [reference_root]``; without an argument the
+root is ``$EPPGCN_REFERENCE_ROOT``, else where the build image mounts the
+reference tree.
 """
 from __future__ import annotations
 
@@ -24,9 +26,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "eppgcn_reference"
 TARGET = os.path.join(OUT, NAME + sysconfig.get_config_var("EXT_SUFFIX"))
+DEFAULT_ROOT = os.environ.get("EPPGCN_REFERENCE_ROOT", "/root/reference")
 
 
-def build(reference_root: str = "/root/reference", force: bool = False, verbose: bool = True) -> str | None:
+def build(reference_root: str = DEFAULT_ROOT, force: bool = False, verbose: bool = True) -> str | None:
     src = os.path.join(reference_root, "EPPGCN", "GCNConv")
     files = [os.path.join(src, f) for f in ("EPPGCN.cpp", "EPPGCN_kernel.cu", "cuCompactor.cu")]
     if not all(os.path.exists(f) for f in files):
@@ -68,4 +71,5 @@ def build(reference_root: str = "/root/reference", force: bool = False, verbose:
 
 
 if __name__ == "__main__":
-    print(build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", force="--force" in sys.argv))
+    print(build(sys.argv[1] if len(sys.argv) > 1 and not sys.argv[1].startswith("--") else DEFAULT_ROOT,
+                force="--force" in sys.argv))

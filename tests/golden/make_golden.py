@@ -4,7 +4,7 @@ seeded inputs.
 
   python tests/golden/make_golden.py            # CPU operators -> ref_cpu_ops.npz
   python tests/golden/make_golden.py --gpu      # on a GPU box: CUDA operators -> ref_gpu_ops.npz
-                                                # (also copied to gpurun_out/ so it travels back)
+  python tests/golden/make_golden.py --gpu --copy-to DIR     # ... and a copy of the file into DIR
 
 Inputs are regenerated from seeds by ``golden_inputs()``; only the reference's
 outputs are stored.  Cases stay inside the reference's valid range: at most
@@ -121,8 +121,10 @@ def make_gpu(ref):
     torch.cuda.synchronize()
     path = os.path.join(HERE, "ref_gpu_ops.npz")
     np.savez_compressed(path, **out)
-    os.makedirs(os.path.join(ROOT, "gpurun_out"), exist_ok=True)
-    shutil.copy(path, os.path.join(ROOT, "gpurun_out", "ref_gpu_ops.npz"))
+    if "--copy-to" in sys.argv:
+        target = sys.argv[sys.argv.index("--copy-to") + 1]
+        os.makedirs(target, exist_ok=True)
+        shutil.copy(path, os.path.join(target, "ref_gpu_ops.npz"))
     print("wrote ref_gpu_ops.npz", len(out), "arrays", os.path.getsize(path), "bytes")
 
 

@@ -434,6 +434,9 @@ def main():
     p.add_argument("--chunks", type=int, default=0,
                    help="balanced_halo: column chunks per exchange, one compact source buffer each; 0 = two when "
                         "every layer is at least 32 columns wide (and splits into 16-byte pieces), else one")
+    p.add_argument("--overlap", action="store_true",
+                   help="balanced_halo with the push transport and >1 chunk: push chunk c+1 on a side stream while "
+                        "chunk c is aggregated (not yet measured; off by default)")
     p.add_argument("--transport", default="push", choices=["push", "nccl"],
                    help="balanced_halo: peer stores by this library's kernel, or NCCL all-to-all")
     p.add_argument("--no-cpu-baseline", action="store_true")

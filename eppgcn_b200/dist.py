@@ -297,6 +297,21 @@ class PeerFabric:
             raise RuntimeError(f"a bounded wait for another GPU ran out (status {code}): a rank is late or gone")
 
 
+class _Landed:
+    """What :meth:`DealtHalo.start` hands out per chunk on the push transport:
+    ``wait()`` makes the current stream wait for this rank's push of the chunk
+    (when it ran on the side stream) and then for every rank's, through a
+    barrier.  All ranks wait for the chunks in the same order."""
+
+    def __init__(self, fabric, event=None):
+        self.fabric, self.event = fabric, event
+
+    def wait(self):
+        if self.event is not None:
+            torch.cuda.current_stream().wait_event(self.event)
+        self.fabric.barrier()
+
+
 class DealtHalo:
     """Halo exchange over equal row blocks (the dealt-out relabelling), with the
     rank's own rows kept out of the all-to-all and the transfer cut into column
@@ -312,6 +327,7 @@ class DealtHalo:
         dev = cols.device
         self.rank, self.world, self.group, self.n_loc = rank, world, group, n_loc
         self.fabric = fabric if world > 1 else None
+        self.overlap, self._side = False, None       # push chunk c+1 on a side stream beside the aggregation of chunk c
         ids = cols.long()
         v0 = rank * n_loc
         own = (ids >= v0) & (ids < v0 + n_loc)
@@ -390,16 +406,38 @@ class DealtHalo:
         if self.fabric is not None and isinstance(bufs[0][0], list):
             # peer stores: wait until no rank reads these buffers any more, push, wait until every push has landed
             self.fabric.barrier()
-            for c, (peers, buf) in enumerate(bufs):
-                dc = buf.size(1)
-                own = buf[self.num_remote:]
-                if local is not None:
-                    own.copy_(local[:, c * dc:(c + 1) * dc])
-                wide = _padded_rows(own)
+            if local is not None:
+                for c, (_, buf) in enumerate(bufs):
+                    dc = buf.size(1)
+                    buf[self.num_remote:].copy_(local[:, c * dc:(c + 1) * dc])
+
+            def push(peers, buf):
+                wide = _padded_rows(buf[self.num_remote:])
                 self.fabric.capi.push_rows(wide, self.send_idx32, self.send_ptr, peers, self.peer_first_row,
                                            wide.size(1))
-                out.append((None, buf))
-            self.fabric.barrier()
+
+            if not (self.overlap and len(bufs) > 1):
+                for peers, buf in bufs:
+                    push(peers, buf)
+                    out.append((None, buf))
+                self.fabric.barrier()
+                return out
+            # chunk 0 on this stream; the later chunks on a side stream, each behind the one before it, so that
+            # they travel while the caller aggregates the chunks that have landed
+            main = torch.cuda.current_stream()
+            if self._side is None:
+                self._side = torch.cuda.Stream(device=bufs[0][1].device)
+            push(*bufs[0])
+            out.append((_Landed(self.fabric), bufs[0][1]))
+            ready = torch.cuda.Event()
+            ready.record(main)
+            with torch.cuda.stream(self._side):
+                self._side.wait_event(ready)
+                for peers, buf in bufs[1:]:
+                    push(peers, buf)
+                    done = torch.cuda.Event()
+                    done.record(self._side)
+                    out.append((_Landed(self.fabric, done), buf))
             return out
         for c, (send, buf) in enumerate(bufs):
             dc = send.size(1)
@@ -472,7 +510,7 @@ class DistHotPath:
     """
 
     def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None,
-                 exchange: str = "balanced", chunks: int = 1, transport: str = "push"):
+                 exchange: str = "balanced", chunks: int = 1, transport: str = "push", overlap: bool = False):
         import eppgcn_b200
         from eppgcn_b200 import capi
         self.capi, self.dev, self.rank, self.world, self.group = capi, dev, rank, world, group
@@ -569,9 +607,11 @@ class DistHotPath:
             if transport == "push" and world > 1 and dev.type == "cuda" and dist.get_backend(group) == "nccl":
                 self.fabric = PeerFabric(dev, rank, world, group)
             self.fwd_plan = DealtHalo(self.col, n_loc, rank, world, group, self.fabric)
+            self.fwd_plan.overlap = overlap
             self.col_c = self.fwd_plan.remap
             for p in self.path:
                 plan = DealtHalo(p["edges"][:p["valid"]], n_loc, rank, world, group, self.fabric)
+                plan.overlap = overlap
                 edges_c = torch.zeros_like(p["edges"])
                 edges_c[:p["valid"]] = plan.remap
                 p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.order].contiguous())
@@ -691,7 +731,7 @@ def run_bench(args, rank: int, world: int, dev):
     if chunks <= 0:           # measured on the 64/64/32-column workload: two 32-column buffers aggregate faster than one
         chunks = 2 if min(dims) >= 32 and all(d % 8 == 0 for d in dims) else 1
     hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=chunks,
-                     transport=getattr(args, "transport", "push"))
+                     transport=getattr(args, "transport", "push"), overlap=getattr(args, "overlap", False))
     dealt = mode == "balanced_halo"
     if device_drawn:
         ds.indptr = ds.indices = None           # the shard is all this rank needs from here on
@@ -853,7 +893,10 @@ def run_bench(args, rank: int, world: int, dev):
                                                           f"rows travel, in {hp.chunks} column chunk(s), "
                                                           + ("gathered and stored into the readers' buffers over "
                                                              "NVLink by one kernel of this library, flag barriers "
-                                                             "with bounded waits" if hp.fabric is not None else
+                                                             "with bounded waits"
+                                                             + (", later chunks pushed on a side stream beside the "
+                                                                "aggregation" if getattr(args, "overlap", False) else "")
+                                                             if hp.fabric is not None else
                                                              "by NCCL all-to-all"),
                                          "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
                                                      "NCCL all-gather per aggregation (source-mask rows only for "

@@ -532,13 +532,10 @@ class DistHotPath:
             train_t = torch.zeros(self.n, dtype=torch.bool, device=dev)
             train_t[new_of_old] = ds.train_mask.to(dev)
             del new_of_old
-        else:
-            g = ds.graph
-            degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
-        if on_device:
-            pass
         elif relabel:
             # relabelled graph: equal rows per rank, hubs dealt out; every per-vertex array follows the new ids
+            g = ds.graph
+            degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
             self.new_of_old, n_loc = balanced_relabel(g.indptr, world)
             self.n = n_loc * world
             self.bounds = np.arange(world + 1, dtype=np.int64) * n_loc
@@ -549,6 +546,8 @@ class DistHotPath:
             train_new[self.new_of_old] = train_np
             degrees_np, train_np = deg_new, train_new
         else:
+            g = ds.graph
+            degrees_np, train_np = ds.degrees.cpu().numpy(), ds.train_mask.cpu().numpy()
             self.new_of_old = None
             self.n = g.num_nodes
             self.bounds = edge_balanced_ranges(g.indptr, world)

@@ -50,6 +50,12 @@ import torch
 import torch.distributed as dist
 
 
+def _sync(dev):
+    """Host wait for the device's queued work; nothing to wait for on the CPU (gloo tests)."""
+    if torch.device(dev).type == "cuda":
+        torch.cuda.synchronize(dev)
+
+
 def edge_balanced_ranges(indptr: np.ndarray, world: int) -> np.ndarray:
     """``world + 1`` vertex boundaries; range ``g`` is ``[b[g], b[g+1])`` and
     holds about ``E / world`` edges.  Rows are never split."""
@@ -276,7 +282,7 @@ class PeerFabric:
         flags.zero_()
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.count, self.max_polls = 0, max_polls    # a poll takes about a microsecond: ranks may be ~10 s apart
-        torch.cuda.synchronize(dev)
+        _sync(dev)
         dist.barrier(self.group)                     # every rank's flag words are zero before the first barrier
 
     def alloc(self, shape, dtype=torch.float32):
@@ -568,7 +574,7 @@ class DistHotPath:
         ngh = [torch.zeros(self.n, dtype=torch.bool, device=dev) for _ in range(L - 1)]
         edge_masks = [torch.full((e_loc,), -1, dtype=torch.int32, device=dev) for _ in range(L)]
         node_degs = [torch.zeros(n_loc, dtype=torch.int32, device=dev) for _ in range(L)]
-        torch.cuda.synchronize(dev)
+        _sync(dev)
         t0 = time.perf_counter()
         for i in range(L):
             src = train if i == 0 else ngh[i - 1]
@@ -583,7 +589,7 @@ class DistHotPath:
             ppb, parts = capi.split_parts(node_degs[i], e_loc, back_size)
             self.path.append(dict(id=ids, edges=edges, pp=ppb, parts=parts, valid=valid,
                                   rows=int(torch.count_nonzero(node_degs[i]).item())))
-        torch.cuda.synchronize(dev)
+        _sync(dev)
         self.prep_s = time.perf_counter() - t0
         self.ngh_masks, self.node_degs, self.edge_masks = ngh, node_degs, edge_masks
         self.back_size = back_size
@@ -597,7 +603,7 @@ class DistHotPath:
                 edges_c = torch.zeros_like(p["edges"])
                 edges_c[:p["valid"]] = plan.pos[p["edges"][:p["valid"]].long()]
                 p.update(plan=plan, edges_c=edges_c, deg_c=plan.compact(self.deg, 0.0))
-            torch.cuda.synchronize(dev)
+            _sync(dev)
             self.plan_s = time.perf_counter() - t0
         if exchange == "balanced_halo":
             t0 = time.perf_counter()
@@ -614,7 +620,7 @@ class DistHotPath:
                 edges_c = torch.zeros_like(p["edges"])
                 edges_c[:p["valid"]] = plan.remap
                 p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.order].contiguous())
-            torch.cuda.synchronize(dev)
+            _sync(dev)
             self.plan_s = time.perf_counter() - t0
         elif halo:
             t0 = time.perf_counter()
@@ -625,7 +631,7 @@ class DistHotPath:
                 edges_c = torch.zeros_like(p["edges"])
                 edges_c[:p["valid"]] = plan.remap
                 p.update(plan=plan, edges_c=edges_c, deg_c=self.deg[plan.needed].contiguous())
-            torch.cuda.synchronize(dev)
+            _sync(dev)
             self.plan_s = time.perf_counter() - t0
 
     def gather(self, full, local):

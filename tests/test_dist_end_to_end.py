@@ -1,0 +1,154 @@
+"""The whole multi-rank orchestration on two gloo ranks without a GPU.
+
+``DistHotPath`` is run on CPU tensors with the device entry points replaced by
+a test double built from the oracle (numpy).  Everything around the kernels is
+the real code: relabelling, shards, sharded path marking with the mask
+reduction, compaction and splitting per shard, the exchange plans of every mode
+(re-indexed edge lists, degree vectors in buffer order, column chunks) and the
+collectives.  Each rank's results are checked against the float64 oracle of the
+whole graph.  The kernels themselves are checked on GPUs elsewhere."""
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from tests.test_dist import free_port
+
+
+def _install_oracle_double():
+    """Replaces the five device entry points ``DistHotPath`` calls with numpy
+    restatements that take and return CPU tensors."""
+    from eppgcn_b200 import capi
+    from oracle import epp_oracle as O
+
+    def mask_forward(ids, part_ptr, edge_list, src_mask, ngh_mask, back_edge_mask, node_degs, num_layers, layer,
+                     blockx=4, blocky=16, row_offset=0):
+        n = src_mask.numel()
+        degs = np.zeros(n, dtype=np.int32)
+        degs[row_offset:row_offset + node_degs.numel()] = node_degs.numpy()
+        ngh = ngh_mask.numpy() if ngh_mask is not None else np.zeros(0, dtype=bool)
+        marks = back_edge_mask.numpy()
+        fresh = marks == -1
+        O.mask_forward(ids.numpy().astype(np.int64) + row_offset, part_ptr.numpy(), edge_list.numpy(),
+                       src_mask.numpy(), ngh, marks, degs, num_layers, layer)
+        marks[fresh & (marks != -1)] -= row_offset            # the device kernel records the shard's own row numbers
+        node_degs.copy_(torch.from_numpy(degs[row_offset:row_offset + node_degs.numel()]))
+
+    def compact_mask(edge_mask, col_idx, mode=0):
+        ids, cols, valid = O.compact_back_edge(edge_mask.numpy(), col_idx.numpy())
+        return (torch.from_numpy(np.asarray(ids, dtype=np.int32)), torch.from_numpy(np.asarray(cols, dtype=np.int32)),
+                int(valid))
+
+    def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):
+        pp, parts = O.split_back_part(node_deg.numpy(), num_edges, part_size, out_len=num_edges + 1)
+        return torch.from_numpy(np.asarray(pp, dtype=np.int32)), int(parts)
+
+    def spmm_forward(feat, row_ptr, col_idx, degrees, part_ptr, part2node, part_size=0, dim_worker=32,
+                     warp_per_block=8, out=None, deg_row=None, prescaled=False):
+        ptr, col = row_ptr.numpy().astype(np.int64), col_idx.numpy().astype(np.int64)
+        rows = np.repeat(np.arange(len(ptr) - 1), np.diff(ptr))
+        src = feat.numpy().astype(np.float64)[col]
+        if not prescaled:
+            src = src * degrees.numpy().astype(np.float64)[col][:, None]
+        acc = np.zeros((len(ptr) - 1, feat.size(1)))
+        np.add.at(acc, rows, src)
+        acc *= (degrees if deg_row is None else deg_row).numpy().astype(np.float64)[:len(ptr) - 1, None]
+        out.copy_(torch.from_numpy(acc.astype(np.float32)))
+        return out
+
+    def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts, part_size=0, blockx=4,
+                                blocky=16, out=None, deg_row=None, num_rows=None):
+        valid = int(part_ptr[num_parts]) if num_parts > 0 else 0
+        r, c = ids.numpy()[:valid].astype(np.int64), edge_list.numpy()[:valid].astype(np.int64)
+        dr = (degrees if deg_row is None else deg_row).numpy().astype(np.float64)
+        w = dr[r] * degrees.numpy().astype(np.float64)[c]
+        acc = np.zeros((out.size(0), d_out.size(1)))
+        np.add.at(acc, r, d_out.numpy().astype(np.float64)[c] * w[:, None])
+        out.copy_(torch.from_numpy(acc.astype(np.float32)))
+        return out
+
+    for name, fn in dict(mask_forward=mask_forward, compact_mask=compact_mask, split_parts=split_parts,
+                         spmm_forward=spmm_forward, spmm_backward_compacted=spmm_backward_compacted).items():
+        setattr(capi, name, fn)
+
+
+def _worker(rank, world, port, mode, results):
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        _install_oracle_double()
+        from eppgcn_b200 import dist as D
+        from eppgcn_b200 import graphs
+        from oracle import epp_oracle as O
+        parts = mode.split(":")
+        mode, chunks = parts[0], int((parts[1:2] or ["1"])[0])
+        ds = graphs.load_workload("cora", 0, layers=3)
+        g, n = ds.graph, ds.num_nodes
+        deg, train = ds.degrees.numpy().copy(), ds.train_mask.numpy().copy()
+        hp = D.DistHotPath(ds, torch.device("cpu"), rank, world, back_size=4, exchange=mode, chunks=chunks)
+        sh = hp.shard
+        if hp.new_of_old is not None:
+            old_of_new = np.full(hp.n, -1, dtype=np.int64)
+            old_of_new[hp.new_of_old] = np.arange(n)
+            mine = old_of_new[sh.v0:sh.v1]
+        else:
+            mine = np.arange(sh.v0, sh.v1)
+        have = mine >= 0
+
+        def local_rows(m):
+            out = np.zeros((sh.num_rows, m.shape[1]), dtype=np.float32)
+            out[have] = m[mine[have]]
+            return torch.from_numpy(out)
+
+        def close(got, want):
+            got, want = got.numpy()[have], want[mine[have]]
+            return bool((np.abs(got - want) - (2e-6 + 2e-5 * np.abs(want))).max() <= 0)
+
+        path, _ = O.prepare_execution_path(g.indptr, g.indices, train, 3, hp.part_size, [4, 4, 4])
+        sizes = torch.tensor([p["valid"] for p in hp.path] + [p["parts"] for p in hp.path])
+        dist.all_reduce(sizes)
+        ok = sizes[:3].tolist() == [c["valid_len"] for c in path]
+        rng = np.random.Generator(np.random.PCG64(11))
+        for d in (16, 22):
+            m = rng.standard_normal((n, d)).astype(np.float32)
+            out = torch.empty(sh.num_rows, d)
+            if mode in ("halo", "balanced_halo"):
+                hp.forward_halo(local_rows(m * deg[:, None]), out)
+            else:
+                full = torch.empty(hp.n, d)
+                hp.gather(full, local_rows(m * deg[:, None]))
+                hp.forward(full, out)
+            ok &= close(out, O.spmm_forward(g.indptr, g.indices, deg, m))
+            for i, conv in enumerate(path):
+                d_in = torch.empty(sh.num_rows, d)
+                if "plan" in hp.path[i]:
+                    hp.backward_halo(i, local_rows(m), d_in)
+                else:
+                    full = torch.empty(hp.n, d)
+                    hp.gather(full, local_rows(m))
+                    hp.backward(i, full, d_in)
+                ok &= close(d_in, O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, m,
+                                                            conv["numParts"]))
+        results[rank] = bool(ok)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2"])
+def test_two_gloo_ranks_match_the_whole_graph_oracle(mode):
+    world = 2
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, free_port(), mode, results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True}
+
+
+@pytest.mark.timeout(600)
+def test_three_ranks_and_a_vertex_count_that_does_not_divide(tmp_path):
+    """Cora has 2,708 vertices: three ranks need padding rows in the last block."""
+    world = 3
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, free_port(), "balanced_halo", results), nprocs=world, join=True)
+    assert dict(results) == {0: True, 1: True, 2: True}

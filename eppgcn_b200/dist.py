@@ -285,6 +285,11 @@ class PeerFabric:
         _sync(dev)
         dist.barrier(self.group)                     # every rank's flag words are zero before the first barrier
 
+    @staticmethod
+    def available(dev, group=None) -> bool:
+        """Peer stores need CUDA devices of one node under an NCCL group."""
+        return torch.device(dev).type == "cuda" and dist.get_backend(group) == "nccl"
+
     def alloc(self, shape, dtype=torch.float32):
         """A buffer of the same shape on every rank; returns ``(own tensor, [address of rank r's copy])``."""
         t = self.symm.empty(tuple(shape), dtype=dtype, device=self.dev)
@@ -609,7 +614,7 @@ class DistHotPath:
             t0 = time.perf_counter()
             if transport not in ("push", "nccl"):
                 raise ValueError("transport must be 'push' (peer stores by this package's kernels) or 'nccl'")
-            if transport == "push" and world > 1 and dev.type == "cuda" and dist.get_backend(group) == "nccl":
+            if transport == "push" and world > 1 and PeerFabric.available(dev, group):
                 self.fabric = PeerFabric(dev, rank, world, group)
             self.fwd_plan = DealtHalo(self.col, n_loc, rank, world, group, self.fabric)
             self.fwd_plan.overlap = overlap

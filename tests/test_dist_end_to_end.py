@@ -73,6 +73,57 @@ def _install_oracle_double():
         setattr(capi, name, fn)
 
 
+class SharedFileFabric:
+    """Stand-in for ``PeerFabric`` on CPU ranks of one machine: a buffer is a
+    file in shared memory that every rank maps, "peer addresses" are the mapped
+    tensors themselves, the push is an indexed copy into them and the barrier is
+    the process group's.  Same three members as the real one (``alloc``,
+    ``barrier``, ``capi.push_rows``), so the plans run unchanged."""
+
+    tag = "0"
+
+    def __init__(self, dev, rank, world, group=None):
+        import types
+        self.rank, self.world, self.group = rank, world, group
+        self.count, self.files, self.keep = 0, [], []
+        self.capi = types.SimpleNamespace(push_rows=self.push_rows)
+
+    @staticmethod
+    def available(dev, group=None):
+        return True
+
+    def alloc(self, shape, dtype=torch.float32):
+        import os
+        assert dtype == torch.float32
+        index = len(self.files)
+        names = [f"/dev/shm/eppgcn_test_{self.tag}_{index}_{r}" for r in range(self.world)]
+        own = np.lib.format.open_memmap(names[self.rank], mode="w+", dtype=np.float32, shape=tuple(shape))
+        own[...] = 0
+        own.flush()
+        dist.barrier(self.group)
+        maps = [own if r == self.rank else np.load(names[r], mmap_mode="r+") for r in range(self.world)]
+        dist.barrier(self.group)
+        os.unlink(names[self.rank])                   # the mappings keep the memory alive; nothing is left behind
+        self.files.append(names)
+        self.keep.append(maps)
+        tensors = [torch.from_numpy(m) for m in maps]
+        return tensors[self.rank], tensors
+
+    def push_rows(self, rows, send_idx, send_ptr, peers, first_row, dim):
+        assert rows.size(1) == dim and dim % 4 == 0
+        for r, peer in enumerate(peers):
+            lo, hi = send_ptr[r], send_ptr[r + 1]
+            if hi > lo:
+                peer[first_row[r]:first_row[r] + hi - lo, :dim] = rows[send_idx[lo:hi].long()]
+
+    def barrier(self):
+        self.count += 1
+        dist.barrier(self.group)
+
+    def check(self):
+        pass
+
+
 def _worker(rank, world, port, mode, results):
     dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
     try:
@@ -82,6 +133,9 @@ def _worker(rank, world, port, mode, results):
         from oracle import epp_oracle as O
         parts = mode.split(":")
         mode, chunks = parts[0], int((parts[1:2] or ["1"])[0])
+        if parts[2:3] == ["push"]:                    # the peer-store transport, on files in shared memory
+            SharedFileFabric.tag = str(port)
+            D.PeerFabric = SharedFileFabric
         ds = graphs.load_workload("cora", 0, layers=3)
         g, n = ds.graph, ds.num_nodes
         deg, train = ds.degrees.numpy().copy(), ds.train_mask.numpy().copy()
@@ -129,13 +183,16 @@ def _worker(rank, world, port, mode, results):
                     hp.backward(i, full, d_in)
                 ok &= close(d_in, O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, m,
                                                             conv["numParts"]))
+        if parts[2:3] == ["push"]:
+            ok &= isinstance(hp.fabric, SharedFileFabric) and hp.fabric.count > 0
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2"])
+@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2",
+                                  "balanced_halo:1:push", "balanced_halo:2:push"])
 def test_two_gloo_ranks_match_the_whole_graph_oracle(mode):
     world = 2
     mgr = mp.get_context("spawn").Manager()
@@ -150,5 +207,5 @@ def test_three_ranks_and_a_vertex_count_that_does_not_divide(tmp_path):
     world = 3
     mgr = mp.get_context("spawn").Manager()
     results = mgr.dict()
-    mp.spawn(_worker, args=(world, free_port(), "balanced_halo", results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, free_port(), "balanced_halo:2:push", results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True, 2: True}

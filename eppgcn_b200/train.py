@@ -119,9 +119,13 @@ class GCNTrainer:
             for i in range(L):
                 self.mask_forward(i)
             self.build_back_part()
-            torch.cuda.synchronize(self.device)
+            self._sync()
             self.build_time += time.perf_counter() - t0
         self.for_time = self.loss_time = self.back_time = 0.0
+
+    def _sync(self):
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
 
     # EPPGCN/gcn_main.py:147-149
     def mask_forward(self, i):
@@ -168,7 +172,7 @@ class GCNTrainer:
         t0 = time.perf_counter()
         out = self.forward(x, isFirstIter)
         if timed:
-            torch.cuda.synchronize(self.device)
+            self._sync()
             self.for_time += time.perf_counter() - t0
         if isFirstIter and not self.prepared:
             t0 = time.perf_counter()
@@ -178,12 +182,12 @@ class GCNTrainer:
         logp = F.log_softmax(out, dim=1)
         loss = F.nll_loss(logp[self.ds.train_mask], self.ds.y[self.ds.train_mask])
         if timed:
-            torch.cuda.synchronize(self.device)
+            self._sync()
             self.loss_time += time.perf_counter() - t0
         t0 = time.perf_counter()
         loss.backward()
         if timed:
-            torch.cuda.synchronize(self.device)
+            self._sync()
             self.back_time += time.perf_counter() - t0
         self.optimizer.step()
         return loss

@@ -51,3 +51,33 @@ def assert_close(got, want, rtol=O.RTOL, atol=O.ATOL, what=""):
 def prepared_path(indptr, indices, train_mask, layers, part_size, back_sizes):
     """Oracle preparation, returned per convolution."""
     return O.prepare_execution_path(indptr, indices, train_mask, layers, part_size, back_sizes)
+
+
+def cached_path_scenario(tmp_path, device, make_trainer=None):
+    """Two trainers on the same workload and seed: the first prepares the
+    execution path and writes it to ``tmp_path``, the second must load it and
+    take the same first step.  Shared by the GPU test and by the CPU test that
+    runs the harness on a numpy double of the operator module."""
+    import pytest
+    import torch
+    from eppgcn_b200 import graphs
+    from eppgcn_b200.train import GCNTrainer
+
+    def run():
+        ds = graphs.load_workload("cora", 0)
+        tr = GCNTrainer(ds, hidden=16, backsize_mode="map", prepare_before_training=False, seed=5,
+                        path_cache_dir=str(tmp_path), device=device)
+        losses = [float(tr.train_epoch(i == 0).item()) for i in range(4)]
+        return tr, losses
+
+    first, l1 = run()
+    assert not first.path_from_cache and first.prepared and len(list(tmp_path.iterdir())) == 1
+    second, l2 = run()
+    assert second.path_from_cache and second.prepared
+    for a, b in zip(first.back_props, second.back_props):
+        assert a.numParts == b.numParts and a.partSize == b.partSize and a.valid_len == b.valid_len
+        assert torch.equal(a.id[:a.valid_len], b.id) and torch.equal(a.edgeList[:a.valid_len], b.edgeList)
+        assert torch.equal(a.partPointer[:a.numParts + 1], b.partPointer)
+    # the first step starts from the same weights (atomics may reorder sums); later ones only have to stay sane
+    assert l1[0] == pytest.approx(l2[0], rel=1e-5) and all(np.isfinite(l1 + l2))
+    return first, second

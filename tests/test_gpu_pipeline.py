@@ -180,24 +180,6 @@ def test_timers_print_the_reference_keys(gnna, cuda, capfd):
 
 def test_trainer_reads_a_prepared_path_back_from_disk(cuda, tmp_path):
     """Two trainers on the same workload and seed: the first prepares the path
-    and writes it, the second loads it and must take exactly the same steps."""
-    from eppgcn_b200 import graphs
-    from eppgcn_b200.train import GCNTrainer
-
-    def run():
-        ds = graphs.load_workload("cora", 0)
-        tr = GCNTrainer(ds, hidden=16, backsize_mode="map", prepare_before_training=False, seed=5,
-                        path_cache_dir=str(tmp_path))
-        losses = [float(tr.train_epoch(i == 0).item()) for i in range(4)]
-        return tr, losses
-
-    first, l1 = run()
-    assert not first.path_from_cache and len(list(tmp_path.iterdir())) == 1
-    second, l2 = run()
-    assert second.path_from_cache and second.prepared
-    for a, b in zip(first.back_props, second.back_props):
-        assert a.numParts == b.numParts and a.partSize == b.partSize and a.valid_len == b.valid_len
-        assert torch.equal(a.id[:a.valid_len], b.id) and torch.equal(a.edgeList[:a.valid_len], b.edgeList)
-        assert torch.equal(a.partPointer[:a.numParts + 1], b.partPointer)
-    # the first step starts from the same weights (atomics may reorder sums); later ones only have to stay sane
-    assert l1[0] == pytest.approx(l2[0], rel=1e-5) and all(np.isfinite(l1 + l2))
+    and writes it, the second loads it and must take exactly the same first step."""
+    from tests.helpers import cached_path_scenario
+    cached_path_scenario(tmp_path, "cuda")

@@ -88,3 +88,21 @@ def test_preparing_before_training_gives_the_same_path(cpu_operators):
 def test_prepared_path_is_read_back_from_disk(cpu_operators, tmp_path):
     first, second = cached_path_scenario(tmp_path, "cpu")
     assert second.build_time >= 0.0
+
+
+def test_harness_runs_on_a_graph_read_from_files(cpu_operators, tmp_path):
+    """The reference's file layout (edge list + train mask) through the loader and the harness."""
+    from eppgcn_b200 import loader
+    from eppgcn_b200.train import GCNTrainer
+    rng = np.random.Generator(np.random.PCG64(4))
+    n = 150
+    src, dst = rng.integers(0, n, 900), rng.integers(0, n, 900)
+    src, dst = np.concatenate([src, dst, [n - 1]]), np.concatenate([dst, src, [n - 1]])     # symmetric, ids up to n-1
+    with open(tmp_path / "toy_snap", "w") as f:
+        f.writelines(f"{s} {d}\n" for s, d in zip(src, dst))
+    np.savetxt(tmp_path / "train_mask_0.3", (rng.random(n) < 0.3).astype(int), fmt="%d")
+    ds = loader.load_dataset_files(str(tmp_path), "toy", 0.3, 12, 5, 2, degree_norm="rsqrt")
+    tr = GCNTrainer(ds, hidden=8, backsize_mode="map", prepare_before_training=False, seed=2, device="cpu")
+    losses = [float(tr.train_epoch(i == 0).item()) for i in range(5)]
+    assert tr.prepared and np.isfinite(losses).all() and losses[-1] < losses[0]
+    assert tr.inputInfo.partSize == max(int(ds.avg_degree), 1)

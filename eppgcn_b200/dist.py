@@ -615,7 +615,20 @@ class DistHotPath:
             if transport not in ("push", "nccl"):
                 raise ValueError("transport must be 'push' (peer stores by this package's kernels) or 'nccl'")
             if transport == "push" and world > 1 and PeerFabric.available(dev, group):
-                self.fabric = PeerFabric(dev, rank, world, group)
+                # peer-mapped buffers may be unavailable (no peer access between the devices, allocator support
+                # missing): every rank must then agree to use the NCCL all-to-all instead
+                try:
+                    self.fabric, why = PeerFabric(dev, rank, world, group), ""
+                except Exception as exc:           # noqa: BLE001 - any failure means "no peer stores here"
+                    self.fabric, why = None, repr(exc)
+                agreed = torch.tensor([0 if self.fabric is None else 1], device=dev)
+                dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=group)
+                if int(agreed.item()) == 0:
+                    if rank == 0:
+                        import sys
+                        print("eppgcn_b200.dist: peer-store transport unavailable, using NCCL all-to-all"
+                              + (f" ({why[:200]})" if why else ""), file=sys.stderr, flush=True)
+                    self.fabric = None
             self.fwd_plan = DealtHalo(self.col, n_loc, rank, world, group, self.fabric)
             self.fwd_plan.overlap = overlap
             self.col_c = self.fwd_plan.remap

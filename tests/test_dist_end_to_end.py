@@ -136,6 +136,13 @@ def _worker(rank, world, port, mode, results):
         if parts[2:3] == ["push"]:                    # the peer-store transport, on files in shared memory
             SharedFileFabric.tag = str(port)
             D.PeerFabric = SharedFileFabric
+        if parts[2:3] == ["broken"]:                  # peer buffers fail on one rank only: all ranks must fall back
+            class Broken(SharedFileFabric):
+                def __init__(self, dev, rank, world, group=None):
+                    if rank == 1:
+                        raise RuntimeError("no peer access")
+                    super().__init__(dev, rank, world, group)
+            D.PeerFabric = Broken
         ds = graphs.load_workload("cora", 0, layers=3)
         g, n = ds.graph, ds.num_nodes
         deg, train = ds.degrees.numpy().copy(), ds.train_mask.numpy().copy()
@@ -185,6 +192,8 @@ def _worker(rank, world, port, mode, results):
                                                             conv["numParts"]))
         if parts[2:3] == ["push"]:
             ok &= isinstance(hp.fabric, SharedFileFabric) and hp.fabric.count > 0
+        if parts[2:3] == ["broken"]:
+            ok &= hp.fabric is None
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -192,7 +201,7 @@ def _worker(rank, world, port, mode, results):
 
 @pytest.mark.timeout(600)
 @pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2",
-                                  "balanced_halo:1:push", "balanced_halo:2:push"])
+                                  "balanced_halo:1:push", "balanced_halo:2:push", "balanced_halo:1:broken"])
 def test_two_gloo_ranks_match_the_whole_graph_oracle(mode):
     world = 2
     mgr = mp.get_context("spawn").Manager()

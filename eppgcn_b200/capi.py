@@ -36,7 +36,7 @@ SIGNATURES = {
     "eppgcn_split_scratch_bytes": (_SZ, [_I]),
     "eppgcn_split_parts": (_I, [_P, _I, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
     "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
-    "eppgcn_push_rows": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _P]),
+    "eppgcn_push_rows": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _LL, _P]),
     "eppgcn_peer_barrier": (_I, [_P, _I, _I, C.c_uint, _LL, _P, _P]),
     "eppgcn_build_part_host": (_I, [_I, _P, _I, _P, _P, C.POINTER(_LL)]),
     "eppgcn_map_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
@@ -244,18 +244,19 @@ def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):
     return out, parts
 
 
-def push_rows(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, dim=None):
+def push_rows(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, dim=None, start_row=0):
     """Gathers ``rows[send_idx[j]]`` and stores them into other ranks' buffers
     (``peer_base``: their addresses as mapped into this process).  ``send_ptr``,
     ``peer_base`` and ``peer_first_row`` are Python sequences of length
-    ``world + 1``, ``world`` and ``world``."""
+    ``world + 1``, ``world`` and ``world``; ``start_row`` is the send-list entry
+    the kernel begins with (it wraps around)."""
     world = len(peer_base)
     dim = rows.size(1) if dim is None else dim
     sp = (_LL * (world + 1))(*[int(v) for v in send_ptr])
     pb = (_P * world)(*[int(v) if v else None for v in peer_base])
     fr = (_LL * world)(*[int(v) for v in peer_first_row])
     check(lib().eppgcn_push_rows(rows.data_ptr(), _row_stride(rows, "rows"), _dev(send_idx, torch.int32, "send_idx"),
-                                 sp, pb, fr, int(peer_ld), int(dim), world, _stream()))
+                                 sp, pb, fr, int(peer_ld), int(dim), world, int(start_row), _stream()))
 
 
 def peer_barrier(peer_flags, rank, value, status, max_polls=4_000_000):

@@ -21,15 +21,22 @@ struct PeerTable {
   long long send_ptr[kMaxPeers + 1];// rows [send_ptr[r], send_ptr[r+1]) of the send list go to peer r
 };
 
-// One float4 per thread: send-list entry j, piece q of its row.
+// One float4 per thread: send-list entry j, piece q of its row.  The walk over
+// the send list starts at entry start_row and wraps around, so that the ranks
+// of a group, each starting at its right-hand neighbour's rows, store into
+// different peers at any one time instead of all into rank 0 first.
 __global__ void __launch_bounds__(256) push_rows_kernel(const float *__restrict__ rows, long long rows_ld,
                                                         const int *__restrict__ send_idx, PeerTable t,
-                                                        long long peer_ld, int pieces, int world) {
-  const long long total = t.send_ptr[world] * pieces;
+                                                        long long peer_ld, int pieces, int world,
+                                                        long long start_row) {
+  const long long num_rows = t.send_ptr[world];
+  const long long total = num_rows * pieces;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const long long j = i / pieces;
-    const int q = static_cast<int>(i - j * pieces);
+    const long long j0 = i / pieces;
+    const int q = static_cast<int>(i - j0 * pieces);
+    long long j = j0 + start_row;
+    if (j >= num_rows) j -= num_rows;
     int r = 0;
 #pragma unroll
     for (int k = 1; k < kMaxPeers; ++k) r += (k < world && j >= t.send_ptr[k]) ? 1 : 0;
@@ -80,7 +87,7 @@ __global__ void peer_barrier_kernel(FlagTable t, int rank, int world, unsigned v
 EPP_EXPORT int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
                                 const long long *send_ptr, void *const *peer_base,
                                 const long long *peer_first_row, long long peer_ld, int dim, int world,
-                                void *stream) {
+                                long long start_row, void *stream) {
   EPP_REQUIRE(world >= 1 && world <= epp::kMaxPeers, "world must be 1..16");
   EPP_REQUIRE(dim >= 4 && dim % 4 == 0 && rows_ld % 4 == 0 && peer_ld % 4 == 0 && rows_ld >= dim && peer_ld >= dim,
               "rows must be whole 16-byte pieces");
@@ -93,6 +100,7 @@ EPP_EXPORT int eppgcn_push_rows(const float *rows, long long rows_ld, const int 
   EPP_REQUIRE(send_ptr[0] == 0, "send_ptr must start at 0");
   const long long total_rows = send_ptr[world];
   if (total_rows == 0) return EPP_OK;
+  EPP_REQUIRE(start_row >= 0 && start_row < total_rows, "start_row must be an entry of the send list");
   EPP_REQUIRE(rows && send_idx, "null pointer");
   EPP_REQUIRE((reinterpret_cast<uintptr_t>(rows) % 16) == 0, "rows must be 16-byte aligned");
   for (int r = 0; r < world; ++r) {
@@ -106,7 +114,7 @@ EPP_EXPORT int eppgcn_push_rows(const float *rows, long long rows_ld, const int 
   long long blocks = epp::ceil_div_ll(total_rows * pieces, 256 * 4);
   if (blocks > 148 * 8) blocks = 148 * 8;
   epp::push_rows_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      rows, rows_ld, send_idx, t, peer_ld, pieces, world);
+      rows, rows_ld, send_idx, t, peer_ld, pieces, world, start_row);
   EPP_CHECK_LAUNCH("push_rows_kernel");
   return EPP_OK;
 }

@@ -373,6 +373,8 @@ class DealtHalo:
             dist.all_to_all_single(first_out, first_in, group=group)
             self.peer_first_row = first_out.tolist()
             self.send_ptr = [0] + np.cumsum(self.send_counts).tolist()
+            # every rank starts with its right-hand neighbour's rows, so no peer is everybody's first target
+            self.push_start = self.send_ptr[(rank + 1) % world] % max(self.send_ptr[-1], 1)
             self.send_idx32 = self.send_idx.to(torch.int32)
             rows_max = torch.tensor([self.num_rows], device=dev, dtype=torch.int64)
             dist.all_reduce(rows_max, op=dist.ReduceOp.MAX, group=group)
@@ -425,7 +427,7 @@ class DealtHalo:
             def push(peers, buf):
                 wide = _padded_rows(buf[self.num_remote:])
                 self.fabric.capi.push_rows(wide, self.send_idx32, self.send_ptr, peers, self.peer_first_row,
-                                           wide.size(1))
+                                           wide.size(1), start_row=self.push_start)
 
             if not (self.overlap and len(bufs) > 1):
                 for peers, buf in bufs:

@@ -255,6 +255,11 @@ int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *st
  * is rank r's buffer as mapped into this process (peer access enabled, e.g.
  * a CUDA IPC or fabric mapping), unused when rank r gets no rows.  dim,
  * rows_ld and peer_ld are multiples of 4 floats, all bases 16-byte aligned.
+ * start_row (0 <= start_row < send_ptr[world]) is the send-list entry the
+ * kernel begins with (it wraps around); the result does not depend on it.
+ * Ranks that each start at their right-hand neighbour's rows
+ * (send_ptr[(rank+1) % world]) keep every peer's NVLink ingress busy instead
+ * of all storing into rank 0 first.
  * The caller orders the stores against the readers with eppgcn_peer_barrier.
  *
  * eppgcn_peer_barrier is a barrier over `world` GPUs on flag words in peer
@@ -274,7 +279,7 @@ int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *st
 int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
                      const long long *send_ptr, void *const *peer_base,
                      const long long *peer_first_row, long long peer_ld, int dim, int world,
-                     void *stream);
+                     long long start_row, void *stream);
 int eppgcn_peer_barrier(void *const *peer_flags, int rank, int world, unsigned value,
                         long long max_polls, int *status_dev, void *stream);
 

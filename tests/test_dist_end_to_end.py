@@ -109,8 +109,8 @@ class SharedFileFabric:
         tensors = [torch.from_numpy(m) for m in maps]
         return tensors[self.rank], tensors
 
-    def push_rows(self, rows, send_idx, send_ptr, peers, first_row, dim):
-        assert rows.size(1) == dim and dim % 4 == 0
+    def push_rows(self, rows, send_idx, send_ptr, peers, first_row, dim, start_row=0):
+        assert rows.size(1) == dim and dim % 4 == 0 and 0 <= start_row < max(send_ptr[-1], 1)
         for r, peer in enumerate(peers):
             lo, hi = send_ptr[r], send_ptr[r + 1]
             if hi > lo:

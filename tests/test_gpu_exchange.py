@@ -10,8 +10,9 @@ from eppgcn_b200 import capi
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("start", [0, 700, 1999])
 @pytest.mark.parametrize("dim,pad", [(4, 0), (16, 0), (32, 8), (64, 0)])
-def test_push_rows_places_every_row(cuda, dim, pad):
+def test_push_rows_places_every_row(cuda, dim, pad, start):
     rng = np.random.Generator(np.random.PCG64(dim))
     n, world = 5000, 3
     rows = torch.randn(n, dim + pad, device=cuda)[:, :dim]
@@ -20,7 +21,7 @@ def test_push_rows_places_every_row(cuda, dim, pad):
     send_ptr = [0] + np.cumsum(counts).tolist()
     first = [11, 0, 5]
     bufs = [torch.full((c + first[r] + 3, dim), -1.0, device=cuda) for r, c in enumerate(counts)]
-    capi.push_rows(rows, idx, send_ptr, [b.data_ptr() for b in bufs], first, dim)
+    capi.push_rows(rows, idx, send_ptr, [b.data_ptr() for b in bufs], first, dim, start_row=start)
     torch.cuda.synchronize()
     for r, c in enumerate(counts):
         got = bufs[r]
@@ -34,6 +35,10 @@ def test_push_rows_rejects_ragged_rows(cuda):
     idx = torch.zeros(1, dtype=torch.int32, device=cuda)
     with pytest.raises(capi.EppError) as e:
         capi.push_rows(rows, idx, [0, 1], [rows.data_ptr()], [0], 6)
+    assert e.value.status == capi.EPP_ERR_BAD_ARG
+    wide = torch.randn(8, 8, device=cuda)
+    with pytest.raises(capi.EppError) as e:                     # the walk must start inside the send list
+        capi.push_rows(wide, idx, [0, 1], [wide.data_ptr()], [0], 8, start_row=1)
     assert e.value.status == capi.EPP_ERR_BAD_ARG
 
 

@@ -56,3 +56,40 @@ def test_dataset_bag_layout():
     assert torch.all(ds.y == 1) and ds.y.dtype == torch.long
     ref = graphs.load_workload("cora", 0, degree_norm="sqrt")
     np.testing.assert_allclose(ref.degrees.numpy(), np.sqrt(deg), rtol=1e-6)   # EPPGCN/dataset.py:118-119
+
+
+def test_device_drawn_rmat_is_a_valid_symmetric_csr():
+    """The torch generator behind the large workloads, run on the CPU at a small
+    scale: sorted unique columns, exactly one self loop per vertex, symmetric,
+    and the same graph for the same seed."""
+    import torch
+    indptr, indices = graphs.rmat_csr_device(10, 8, 0.57, 0.19, 0.19, 3, "cpu")
+    again = graphs.rmat_csr_device(10, 8, 0.57, 0.19, 0.19, 3, "cpu")
+    assert torch.equal(indptr, again[0]) and torch.equal(indices, again[1])
+    ip, ix = indptr.numpy().astype(np.int64), indices.numpy().astype(np.int64)
+    n = len(ip) - 1
+    assert n == 1 << 10 and ip[0] == 0 and ip[-1] == len(ix) and indptr.dtype == torch.int32
+    rows = np.repeat(np.arange(n), np.diff(ip))
+    key = rows * n + ix
+    assert np.all(np.diff(key) > 0)                                  # sorted within rows, no repeated pair
+    assert np.array_equal(np.sort(ix * n + rows), key)               # every pair has its mirror
+    assert int((rows == ix).sum()) == n                              # one self loop per vertex
+    assert len(ix) > 8 * n                                           # most of the 2 * 8 * n draws survive
+
+
+def test_file_csr_matches_scipy_on_random_lists():
+    from hypothesis import given, settings, strategies as st
+    from scipy.sparse import coo_matrix
+    from eppgcn_b200 import loader
+
+    @settings(max_examples=40, deadline=None)
+    @given(st.integers(1, 60), st.integers(0, 400), st.integers(0, 10_000))
+    def check(n, e, seed):
+        rng = np.random.Generator(np.random.PCG64(seed))
+        src, dst = rng.integers(0, n, e), rng.integers(0, n, e)
+        indptr, indices = loader.csr_from_directed(n, src, dst)
+        ref = coo_matrix((np.ones(e), (src, dst)), shape=(n, n)).tocsr()
+        ref.sort_indices()
+        assert np.array_equal(indptr, ref.indptr) and np.array_equal(indices, ref.indices)
+
+    check()

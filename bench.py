@@ -402,6 +402,11 @@ def run_reference(args):
         return
     from eppgcn_b200 import graphs
     spec = graphs.WORKLOADS[args.workload]
+    if spec.get("draw") == "device":
+        print(json.dumps({"impl": "reference", "unavailable": f"{args.workload} is drawn on the GPU (its host "
+                          "generation takes too long for a bench run); the CPU arm covers the host-drawn workloads"}),
+              flush=True)
+        return
     graph = graphs.make_graph(args.workload, args.seed)
     dims = [spec["hidden"], spec["classes"]]
     ms, cores, epochs = run_cpu(graph, dims, args.steps, args.warmup, budget_s=90.0)

@@ -19,12 +19,13 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libeppgcn_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
+PROBE_PATH = os.path.join(HERE, "libeppgcn_probe.so")
 EXT_NAME = "GNNAdvisor"
 EXT_PATH = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-              "--use_fast_math=false", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
-LIB_SOURCES = ["spmm.cu", "update.cu", "prep.cu", "exchange.cu", "host.cu"]
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+LIB_SOURCES = ["spmm.cu", "segment_spmm.cu", "update.cu", "prep.cu", "exchange.cu", "host.cu"]
 
 
 def _nvcc() -> str:
@@ -53,14 +54,23 @@ def _run(cmd: list[str], verbose: bool):
 
 def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
     srcs = [os.path.join(CSRC, s) for s in LIB_SOURCES]
-    deps = srcs + [os.path.join(CSRC, "common.cuh"),
+    deps = srcs + [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "rowio.cuh"),
                    os.path.join(HERE, "..", "include", "eppgcn_b200.h"), __file__]
     if force or _stale(LIB_PATH, deps):
-        flags = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+        flags = list(NVCC_FLAGS)
         if ptxas_info:
             flags += ["-Xptxas", "-v"]
         _run([_nvcc(), *flags, "-shared", "-o", LIB_PATH, *srcs], verbose or ptxas_info)
     return LIB_PATH
+
+
+def build_probe(force: bool = False, verbose: bool = False) -> str:
+    """The benchmark's measurement aid (bare gather), a library of its own:
+    nothing in the package loads it."""
+    src = os.path.join(CSRC, "bench", "gather_probe.cu")
+    if force or _stale(PROBE_PATH, [src, os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "rowio.cuh"), __file__]):
+        _run([_nvcc(), *NVCC_FLAGS, "-shared", "-o", PROBE_PATH, src], verbose)
+    return PROBE_PATH
 
 
 def build_extension(force: bool = False, verbose: bool = False) -> str:
@@ -94,6 +104,7 @@ def build_extension(force: bool = False, verbose: bool = False) -> str:
 def build_all(force: bool = False, verbose: bool = False):
     build_library(force, verbose)
     build_extension(force, verbose)
+    build_probe(force, verbose)
 
 
 if __name__ == "__main__":

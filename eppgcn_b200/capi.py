@@ -12,8 +12,7 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# EPPGCN_B200_LIB points at another build of the same library (an experimental kernel variant).
-LIB_PATH = os.environ.get("EPPGCN_B200_LIB") or os.path.join(_HERE, "libeppgcn_b200.so")
+LIB_PATH = os.path.join(_HERE, "libeppgcn_b200.so")
 
 EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE, EPP_ERR_PEER_TIMEOUT = range(6)
 
@@ -28,7 +27,12 @@ SIGNATURES = {
     "eppgcn_spmm_backward_compacted": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
-    "eppgcn_probe_gather": (_I, [_P, _LL, _P, _LL, _I, _P, _P]),
+    "eppgcn_segment_plan_bytes": (_SZ, [_LL, _I]),
+    "eppgcn_segment_plan_from_csr": (_I, [_P, _P, _SZ, _P, _I, _LL, _I, _P]),
+    "eppgcn_segment_plan_from_ids": (_I, [_P, _P, _SZ, _P, _LL, _I, _I, _P]),
+    "eppgcn_segment_plan_destroy": (None, [_P]),
+    "eppgcn_segment_plan_info": (_I, [_P, _P]),
+    "eppgcn_spmm_segments": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _I, _I, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
@@ -169,13 +173,65 @@ def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts,
     return out
 
 
-def probe_gather(col_idx, feat, sink=None):
-    """Enqueues the bare gather of ``feat`` rows over ``col_idx`` (a measurement aid)."""
-    if sink is None:
-        sink = torch.zeros(1, device=feat.device)
-    check(lib().eppgcn_probe_gather(_dev(col_idx, torch.int32, "col_idx"), col_idx.numel(), feat.data_ptr(),
-                                    _row_stride(feat, "feat"), feat.size(1), sink.data_ptr(), _stream()))
-    return sink
+class SegmentPlan:
+    """Plan of the chunked aggregation (``eppgcn_segment_plan_*``): where rows
+    start in an edge list.  Owns the device buffer the library writes the plan
+    into and the host handle; both go when the object does."""
+
+    INFO = ("edges", "rows", "chunks", "chunks_per_warp", "nonempty_rows", "cleared_rows", "implicit_row_ids",
+            "clears_whole_result")
+
+    def __init__(self, handle, buf, dim):
+        self._handle, self._buf, self.dim = handle, buf, dim
+        out = (_LL * 8)()
+        check(lib().eppgcn_segment_plan_info(handle, out))
+        self.info = dict(zip(self.INFO, [int(v) for v in out]))
+
+    @staticmethod
+    def _buffer(index, num_edges, num_rows):
+        if not index.is_cuda or index.dtype != torch.int32 or not index.is_contiguous():
+            raise RuntimeError("the plan is built from a contiguous int32 CUDA tensor")
+        nbytes = lib().eppgcn_segment_plan_bytes(int(num_edges), int(num_rows))
+        return torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=index.device), nbytes
+
+    @classmethod
+    def from_csr(cls, row_ptr, num_edges, dim):
+        """Forward plan: row ``r`` owns edges ``[row_ptr[r], row_ptr[r+1])``."""
+        num_rows = row_ptr.numel() - 1
+        buf, nbytes = cls._buffer(row_ptr, num_edges, num_rows)
+        handle = _P()
+        check(lib().eppgcn_segment_plan_from_csr(C.byref(handle), buf.data_ptr(), nbytes, row_ptr.data_ptr(),
+                                                 num_rows, int(num_edges), int(dim), _stream()))
+        return cls(handle, buf, dim)
+
+    @classmethod
+    def from_ids(cls, ids, num_edges, num_rows, dim):
+        """Backward plan: ``ids[e]`` is the (non-decreasing) row of compacted edge ``e < num_edges``."""
+        buf, nbytes = cls._buffer(ids, num_edges, num_rows)
+        handle = _P()
+        check(lib().eppgcn_segment_plan_from_ids(C.byref(handle), buf.data_ptr(), nbytes, ids.data_ptr(),
+                                                 int(num_edges), int(num_rows), int(dim), _stream()))
+        return cls(handle, buf, dim)
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and _lib is not None:
+            _lib.eppgcn_segment_plan_destroy(self._handle)
+            self._handle = None
+
+
+def spmm_segments(src, col_idx, plan, row_scale=None, out=None, hub_rows=0):
+    """``out[r] = row_scale[r] * sum_e src[col_idx[e]]`` over the rows of ``plan``;
+    ``src`` rows already carry their source-side factor and may be padded."""
+    n = plan.info["rows"]
+    dim = src.size(1)
+    ld = _row_stride(src, "src")
+    if out is None:
+        out = torch.empty(n, dim, device=src.device, dtype=torch.float32)
+    check(lib().eppgcn_spmm_segments(
+        _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), ld,
+        _dev(col_idx, torch.int32, "col_idx"), plan._handle,
+        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, int(hub_rows), _stream()))
+    return out
 
 
 def mask_forward(ids, part_ptr, edge_list, src_mask, ngh_mask, back_edge_mask, node_degs,

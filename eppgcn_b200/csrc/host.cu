@@ -8,7 +8,7 @@
 #include <mutex>
 #include <vector>
 
-#include "common.cuh"
+#include "rowio.cuh"
 
 namespace epp {
 
@@ -19,6 +19,31 @@ void set_error(const char *fmt, ...) {
   va_start(ap, fmt);
   vsnprintf(g_error, sizeof(g_error), fmt, ap);
   va_end(ap);
+}
+
+static std::mutex g_launch_mu;
+
+int smem_opt_in(SmemOptIn &memo, const void *kernel, int smem) {
+  if (smem <= 48 * 1024) return EPP_OK;
+  int dev = 0;
+  EPP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= SmemOptIn::kMaxDevices) {
+    set_error("device ordinal %d is beyond the %d devices this library tracks", dev, SmemOptIn::kMaxDevices);
+    return EPP_ERR_TOO_LARGE;
+  }
+  std::lock_guard<std::mutex> lock(g_launch_mu);
+  if (memo.granted[dev] < smem) {
+    EPP_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    memo.granted[dev] = smem;
+  }
+  return EPP_OK;
+}
+
+int device_sm_count(int *num_sms) {
+  int dev = 0;
+  EPP_CUDA_TRY(cudaGetDevice(&dev));
+  EPP_CUDA_TRY(cudaDeviceGetAttribute(num_sms, cudaDevAttrMultiProcessorCount, dev));
+  return EPP_OK;
 }
 
 namespace {
@@ -164,6 +189,9 @@ EPP_EXPORT int eppgcn_get_ginfo_host(const int *node_deg, int num_nodes, int val
     else ++h[9];
   }
   const int valid_node = static_cast<int>(h[0]);
+  // The reference divides by valid_node unguarded (EPPGCN.cpp:378-384); an
+  // entry point that never takes the process down reports the empty path instead.
+  EPP_REQUIRE(valid_node > 0, "no active vertex");
   out10[0] = static_cast<float>(valid_node * 1.0 / 10000);
   out10[1] = static_cast<float>(valid_len * 1.0 / 10000);
   out10[2] = static_cast<float>(1.0 * valid_len / valid_node);

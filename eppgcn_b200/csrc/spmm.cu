@@ -27,12 +27,12 @@
 // same row are combined with a segmented shuffle reduction, and only the head
 // of each run touches memory: a plain vector store when the run covers the
 // whole row, a vector atomic add otherwise (a row split across warps).
-#include "common.cuh"
+#include <mutex>
+
+#include "rowio.cuh"
 
 namespace epp {
 namespace {
-
-inline bool aligned(const void *p, size_t bytes) { return (reinterpret_cast<uintptr_t>(p) % bytes) == 0; }
 
 template <int VEC>
 __device__ __forceinline__ void load_vec(const float *p, float (&v)[VEC]) {
@@ -44,37 +44,6 @@ __device__ __forceinline__ void load_vec(const float *p, float (&v)[VEC]) {
     v[0] = t.x; v[1] = t.y;
   } else {
     v[0] = __ldg(p);
-  }
-}
-
-// Writes n (<= VEC) floats starting at p with the widest store `ovec` allows.
-template <int VEC>
-__device__ __forceinline__ void store_row(float *p, const float (&v)[VEC], int n, int ovec) {
-  if (VEC == 4 && ovec == 4 && n == 4) {
-    *reinterpret_cast<float4 *>(p) = make_float4(v[0], v[1], v[2], v[3]);
-  } else if (VEC >= 2 && ovec >= 2) {
-#pragma unroll
-    for (int i = 0; i + 1 < VEC; i += 2)
-      if (i + 1 < n) *reinterpret_cast<float2 *>(p + i) = make_float2(v[i], v[i + 1]);
-  } else {
-#pragma unroll
-    for (int i = 0; i < VEC; ++i)
-      if (i < n) p[i] = v[i];
-  }
-}
-
-template <int VEC>
-__device__ __forceinline__ void add_row(float *p, const float (&v)[VEC], int n, int ovec) {
-  if (VEC == 4 && ovec == 4 && n == 4) {
-    atomicAdd(reinterpret_cast<float4 *>(p), make_float4(v[0], v[1], v[2], v[3]));
-  } else if (VEC >= 2 && ovec >= 2) {
-#pragma unroll
-    for (int i = 0; i + 1 < VEC; i += 2)
-      if (i + 1 < n) atomicAdd(reinterpret_cast<float2 *>(p + i), make_float2(v[i], v[i + 1]));
-  } else {
-#pragma unroll
-    for (int i = 0; i < VEC; ++i)
-      if (i < n) atomicAdd(p + i, v[i]);
   }
 }
 
@@ -322,11 +291,15 @@ staged_spmm_kernel(const GroupArgs a, const int cols, const int slab, const int 
   cp_async_wait<0>();
 }
 
+// Launch geometry of one kernel instantiation, remembered per device: the
+// shared-memory opt-in is a per-device attribute and the occupancy answer
+// belongs to the device that gave it.
 struct LaunchInfo {
   int blocks_per_sm = 0;
   int smem = -1;
   int num_sms = 0;
 };
+constexpr int kMaxDevices = 64;
 
 template <int VEC, int LPR, int T, bool HASW>
 int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
@@ -336,18 +309,29 @@ int launch_staged(const GroupArgs &a0, int part_size, cudaStream_t s) {
   const long long want = static_cast<long long>(G) * ps + 8;
   const int slab = static_cast<int>(want > 1024 ? 1024 : (want + 3) / 4 * 4);
   const int smem = slab * 2 * 8 * static_cast<int>(sizeof(int));
-  static LaunchInfo info;              // per instantiation; the occupancy query is repeated when smem changes
-  if (info.smem != smem) {
-    int dev = 0;
-    EPP_CUDA_TRY(cudaGetDevice(&dev));
-    EPP_CUDA_TRY(cudaDeviceGetAttribute(&info.num_sms, cudaDevAttrMultiProcessorCount, dev));
-    if (smem > 48 * 1024)
-      EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, T, HASW>,
-                                        cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&info.blocks_per_sm,
-                                                               staged_spmm_kernel<VEC, LPR, T, HASW>, 256, smem));
-    if (info.blocks_per_sm < 1) info.blocks_per_sm = 1;
-    info.smem = smem;
+  static LaunchInfo per_device[kMaxDevices];   // per instantiation and device
+  static std::mutex mu;
+  int dev = 0;
+  EPP_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error("device ordinal %d is beyond the %d devices this library tracks", dev, kMaxDevices);
+    return EPP_ERR_TOO_LARGE;
+  }
+  LaunchInfo info;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    LaunchInfo &slot = per_device[dev];
+    if (slot.smem != smem) {             // first launch on this device, or another slab size
+      EPP_CUDA_TRY(cudaDeviceGetAttribute(&slot.num_sms, cudaDevAttrMultiProcessorCount, dev));
+      if (smem > 48 * 1024)
+        EPP_CUDA_TRY(cudaFuncSetAttribute(staged_spmm_kernel<VEC, LPR, T, HASW>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+      EPP_CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&slot.blocks_per_sm,
+                                                                 staged_spmm_kernel<VEC, LPR, T, HASW>, 256, smem));
+      if (slot.blocks_per_sm < 1) slot.blocks_per_sm = 1;
+      slot.smem = smem;
+    }
+    info = slot;
   }
   const long long nsets = ceil_div_ll(a0.num_parts, G);
   long long blocks = ceil_div_ll(nsets, 8);
@@ -394,6 +378,8 @@ __global__ void __launch_bounds__(256) zero_column_block_kernel(float *out, long
   }
 }
 
+}  // namespace
+
 int zero_column_block(float *out, long long out_ld, int dim, long long num_rows, cudaStream_t s) {
   int w = 1;
   if (dim % 4 == 0 && out_ld % 4 == 0 && aligned(out, 16)) w = 4;
@@ -408,6 +394,8 @@ int zero_column_block(float *out, long long out_ld, int dim, long long num_rows,
   EPP_CHECK_LAUNCH("zero_column_block_kernel");
   return EPP_OK;
 }
+
+namespace {
 
 template <bool HASW>
 int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) {
@@ -437,68 +425,8 @@ int launch_group_spmm(GroupArgs a, int num_rows, int part_size, cudaStream_t s) 
   }
 }
 
-// Diagnostic: the bare gather of the aggregation -- every edge's source row is
-// fetched (4 lanes per row, 16-byte loads, eight rows in flight per lane) and
-// summed into a value nobody reads.  No weights, no output rows, column ids read
-// straight from global memory.  Its time is the floor for any kernel that has
-// to perform these gathers on this GPU.
-template <int T>
-__global__ void __launch_bounds__(256) gather_probe_kernel(const int *__restrict__ col, long long num_edges,
-                                                           const float *__restrict__ feat, unsigned ld_bytes,
-                                                           int dim, float *sink) {
-  constexpr int CH = 64;                       // edges per 4-lane group
-  const long long q = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 2;
-  const int sl = threadIdx.x & 3;
-  const long long beg = q * CH;
-  const long long end = beg + CH < num_edges ? beg + CH : num_edges;
-  constexpr int U = T >= 8 ? 1 : 8 / T;
-  float acc = 0.f;
-  const char *fb = reinterpret_cast<const char *>(feat + sl * 4);
-  for (long long e = beg; e + U <= end; e += U) {
-    int c[U];
-    float4 v[U][T];
-#pragma unroll
-    for (int u = 0; u < U; ++u) c[u] = __ldg(col + e + u);
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < T; ++k)
-        v[u][k] = (sl * 4 + k * 16 < dim)
-                      ? __ldg(reinterpret_cast<const float4 *>(fb + static_cast<unsigned long long>(
-                                  static_cast<unsigned>(c[u])) * ld_bytes + k * 64))
-                      : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int k = 0; k < T; ++k) acc += v[u][k].x + v[u][k].y + v[u][k].z + v[u][k].w;
-  }
-  if (acc == 1.2345e-30f) *sink = acc;         // keeps the loads alive
-}
-
 }  // namespace
 }  // namespace epp
-
-EPP_EXPORT int eppgcn_probe_gather(const int *col_idx, long long num_edges, const float *feat, long long feat_ld,
-                                   int dim, float *sink, void *stream) {
-  using namespace epp;
-  EPP_REQUIRE(num_edges >= 0 && dim >= 1 && dim <= 128, "sizes out of range (dim 1..128)");
-  EPP_REQUIRE(feat_ld % 4 == 0 && feat_ld >= (dim + 3) / 4 * 4 && feat_ld <= 0x3fffffffLL, "rows must be padded to 16 bytes");
-  if (num_edges == 0) return EPP_OK;
-  EPP_REQUIRE(col_idx && feat && sink && aligned(feat, 16), "null or misaligned pointer");
-  const long long quads = ceil_div_ll(num_edges, 64);
-  const long long blocks = ceil_div_ll(quads * 4, 256);
-  if (blocks > 0x7fffffffLL) return EPP_ERR_TOO_LARGE;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const unsigned ldb = static_cast<unsigned>(feat_ld) * 4u;
-  const int tiles = (dim + 15) / 16;
-  const unsigned grid = static_cast<unsigned>(blocks);
-  if (tiles <= 1) gather_probe_kernel<1><<<grid, 256, 0, s>>>(col_idx, num_edges, feat, ldb, dim, sink);
-  else if (tiles <= 2) gather_probe_kernel<2><<<grid, 256, 0, s>>>(col_idx, num_edges, feat, ldb, dim, sink);
-  else if (tiles <= 4) gather_probe_kernel<4><<<grid, 256, 0, s>>>(col_idx, num_edges, feat, ldb, dim, sink);
-  else gather_probe_kernel<8><<<grid, 256, 0, s>>>(col_idx, num_edges, feat, ldb, dim, sink);
-  EPP_CHECK_LAUNCH("gather_probe_kernel");
-  return EPP_OK;
-}
 
 EPP_EXPORT int eppgcn_spmm_forward(float *out, long long out_ld, const float *feat, long long feat_ld,
                                    const int *row_ptr, const int *col_idx,

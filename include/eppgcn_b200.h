@@ -101,6 +101,61 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
                                    void *stream);
 
 /* ------------------------------------------------------------------------
+ * Planned aggregation: the same sums as eppgcn_spmm_forward (called with
+ * deg_col == NULL) and eppgcn_spmm_backward_compacted, i.e. the work of
+ * spmm_forward_cuda_kernel / ours_backward_cuda_kernel
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:204-295, :626-670), computed over fixed
+ * chunks of 64 edges from a plan that is prepared once per edge list.  The
+ * reference has no such object; it replaces the per-call zero-fill
+ * (EPPGCN_kernel.cu:150, :562) and the per-group atomics (:289-293, :666-668):
+ * the result is written once, rows are summed with atomics only where they
+ * cross a warp's 512-edge span.
+ *
+ *   out[r][:] = row_scale[r] * sum over edges e of row r:  src[col_idx[e]][:]
+ *
+ * A plan describes where rows start in the edge list.  It is built from
+ *   - a CSR row pointer (forward: row r owns edges [row_ptr[r], row_ptr[r+1])), or
+ *   - a row id per edge, non-decreasing (backward: the `ids` array that
+ *     eppgcn_compact_mask produced, valid prefix only).
+ * eppgcn_segment_plan_bytes gives the size of the device buffer the caller
+ * supplies (256-byte aligned; it must outlive the plan); the builder enqueues
+ * a few small kernels on `stream` and synchronises that stream once to read
+ * two counts back.  The plan handle itself is a small host object, freed by
+ * eppgcn_segment_plan_destroy.  `dim` selects the row-width class the plan
+ * serves (<= 32 columns, <= 64, wider): eppgcn_spmm_segments rejects a plan
+ * of another class.  eppgcn_segment_plan_info: out8 = {edges, rows, chunks,
+ * chunks per warp, non-empty rows, rows cleared per call, row ids implicit,
+ * whole result cleared per call}.
+ *
+ * eppgcn_spmm_segments:
+ * out       rows of out_ld floats (0 = dense [rows][dim]); columns 0..dim-1 of
+ *           every row are written (rows without edges come back zero).
+ * src       source rows, already multiplied by their source-side factor
+ *           (eppgcn_update_scaled does that for the forward); row stride
+ *           src_ld a multiple of 4 floats, base 16-byte aligned.
+ * col_idx   the edge list's source row per edge (positions into src),
+ *           16-byte aligned.
+ * row_scale destination-side factor per row id, or NULL for 1.
+ * hub_rows  0, or a number of leading rows of src that every thread block
+ *           copies into shared memory and serves from there
+ *           (hub_rows * src_ld * 4 <= 200 KiB); pays when the producer of src
+ *           places the most referenced rows first.
+ */
+typedef struct eppgcn_segment_plan eppgcn_segment_plan;
+size_t eppgcn_segment_plan_bytes(long long num_edges, int num_rows);
+int eppgcn_segment_plan_from_csr(eppgcn_segment_plan **plan, void *dev_buf, size_t dev_bytes,
+                                 const int *row_ptr, int num_rows, long long num_edges, int dim,
+                                 void *stream);
+int eppgcn_segment_plan_from_ids(eppgcn_segment_plan **plan, void *dev_buf, size_t dev_bytes,
+                                 const int *ids, long long num_edges, int num_rows, int dim,
+                                 void *stream);
+void eppgcn_segment_plan_destroy(eppgcn_segment_plan *plan);
+int eppgcn_segment_plan_info(const eppgcn_segment_plan *plan, long long *out8);
+int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long long src_ld,
+                         const int *col_idx, const eppgcn_segment_plan *plan, const float *row_scale,
+                         int dim, int hub_rows, void *stream);
+
+/* ------------------------------------------------------------------------
  * Dense update of a layer with the source-side factor folded in.
  * Replaces the torch::mm(input, weight) of the forward wrapper
  * (EPPGCN/GCNConv/EPPGCN_kernel.cu:142) for narrow outputs.
@@ -282,18 +337,6 @@ int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
                      long long start_row, void *stream);
 int eppgcn_peer_barrier(void *const *peer_flags, int rank, int world, unsigned value,
                         long long max_polls, int *status_dev, void *stream);
-
-/* ------------------------------------------------------------------------
- * Measurement aid, no counterpart in the reference: performs only the gather
- * of an aggregation -- for every entry of col_idx the fp32 row
- * feat[col_idx[e]][0..dim) is loaded (16-byte loads) and discarded.  No
- * weights, no result.  Its duration is the floor for any aggregation over the
- * same column stream and row width on the device at hand; bench.py reports it
- * beside the kernels' times.  dim <= 128; rows 16-byte aligned (feat_ld a
- * multiple of 4 floats, >= dim rounded up to 4).  sink: one device float.
- */
-int eppgcn_probe_gather(const int *col_idx, long long num_edges, const float *feat, long long feat_ld,
-                        int dim, float *sink, void *stream);
 
 /* ------------------------------------------------------------------------
  * Host-side helpers (CPU pointers, synchronous).

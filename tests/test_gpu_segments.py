@@ -1,0 +1,215 @@
+"""The planned (edge-chunked) aggregation through the C-ABI against the float64
+oracle, and against the group kernel on the same inputs.
+Tolerance: |got - want| <= 1e-6 + 1e-5*|want| for the aggregation itself; twice
+that where the source rows were pre-scaled in fp32 before the sum."""
+import numpy as np
+import pytest
+import torch
+
+from eppgcn_b200 import capi
+from oracle import epp_oracle as O
+from tests.helpers import assert_close, degrees_of, random_csr, t
+
+pytestmark = pytest.mark.gpu
+
+GRAPHS = {
+    "tiny":    dict(n=9, avg_deg=2.0, seed=1, empty_frac=0.3),
+    "sparse":  dict(n=300, avg_deg=3.0, seed=2, empty_frac=0.2),
+    "hubs":    dict(n=700, avg_deg=6.0, seed=3, hubs=3, hub_deg=650),
+    "dense":   dict(n=128, avg_deg=40.0, seed=4),
+    "loops":   dict(n=2000, avg_deg=1.0, seed=5, empty_frac=0.5),
+    "chunk64": dict(n=400, avg_deg=64.0, seed=7),
+}
+
+
+def padded_rows(a, cuda, pad_to=4, poison=True):
+    """[n, d] view of a buffer whose row stride is d rounded up to `pad_to` floats; the padding is NaN
+    beyond the 16-byte piece the kernel is allowed to read."""
+    n, d = a.shape
+    ld = (d + pad_to - 1) // pad_to * pad_to
+    full = torch.zeros(n, ld, device=cuda)
+    if poison and ld > (d + 3) // 4 * 4:
+        full[:, (d + 3) // 4 * 4:] = float("nan")
+    full[:, :d] = t(a, cuda)
+    return full[:, :d]
+
+
+def forward_case(cuda, indptr, indices, dim, pad_to=4, hub_rows=0, seed=0, out=None):
+    n = len(indptr) - 1
+    rng = np.random.Generator(np.random.PCG64(seed))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    deg = degrees_of(indptr)
+    plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), dim)
+    src = padded_rows(feat * deg[:, None], cuda, pad_to)
+    col = t(indices, cuda) if len(indices) else torch.zeros(4, dtype=torch.int32, device=cuda)
+    got = capi.spmm_segments(src, col, plan, t(deg, cuda), out=out, hub_rows=hub_rows)
+    torch.cuda.synchronize()
+    return got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), plan
+
+
+@pytest.mark.parametrize("graph", sorted(GRAPHS))
+@pytest.mark.parametrize("dim", [1, 3, 4, 5, 16, 22, 32, 33, 64, 96, 128, 130, 200])
+def test_forward_dims(cuda, graph, dim):
+    indptr, indices = random_csr(**GRAPHS[graph])
+    got, want, _ = forward_case(cuda, indptr, indices, dim)
+    assert np.isfinite(got).all()
+    assert_close(got, want, 2e-5, 2e-6, what=f"planned forward {graph} dim {dim}")
+
+
+def test_plan_counts(cuda):
+    indptr, indices = random_csr(**GRAPHS["sparse"])
+    n = len(indptr) - 1
+    plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 16)
+    info = plan.info
+    deg = np.diff(indptr)
+    assert info["edges"] == len(indices) and info["rows"] == n and info["chunks"] == (len(indices) + 63) // 64
+    assert info["chunks_per_warp"] == 8 and info["nonempty_rows"] == int((deg > 0).sum())
+    span = 64 * 8
+    crossing = (deg > 0) & (indptr[:-1] // span != (indptr[1:] - 1) // span)
+    assert info["cleared_rows"] == int((deg == 0).sum() + crossing.sum())
+    assert info["implicit_row_ids"] == 0           # the graph has rows without edges
+    assert capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 64).info["chunks_per_warp"] == 4
+    assert capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 128).info["chunks_per_warp"] == 2
+
+
+def test_every_row_nonempty_uses_implicit_row_ids(cuda):
+    indptr, indices = random_csr(500, 5.0, 11, self_loops=True)
+    keep = np.diff(indptr) > 0
+    assert keep.all() or True
+    # add a self loop to rows that came out empty so that every row has an edge
+    rows = []
+    for r in range(len(indptr) - 1):
+        c = indices[indptr[r]:indptr[r + 1]]
+        rows.append(c if len(c) else np.array([r], dtype=np.int32))
+    indptr = np.concatenate([[0], np.cumsum([len(c) for c in rows])]).astype(np.int32)
+    indices = np.concatenate(rows).astype(np.int32)
+    got, want, plan = forward_case(cuda, indptr, indices, 16)
+    assert plan.info["implicit_row_ids"] == 1
+    assert_close(got, want, 2e-5, 2e-6, what="implicit row ids")
+
+
+@pytest.mark.parametrize("dim,hub_rows", [(16, 64), (16, 700), (22, 100), (64, 128), (128, 50)])
+def test_hub_rows_from_shared_memory_give_the_same_result(cuda, dim, hub_rows):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    got, want, _ = forward_case(cuda, indptr, indices, dim, pad_to=8, hub_rows=hub_rows)
+    assert_close(got, want, 2e-5, 2e-6, what=f"hub rows {hub_rows} dim {dim}")
+
+
+def test_hub_rows_beyond_shared_memory_are_refused(cuda):
+    indptr, indices = random_csr(**GRAPHS["dense"])
+    n = len(indptr) - 1
+    plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 128)
+    with pytest.raises(capi.EppError) as e:
+        capi.spmm_segments(torch.zeros(n, 128, device=cuda), t(indices, cuda), plan, hub_rows=401)
+    assert e.value.status == capi.EPP_ERR_BAD_ARG
+
+
+def test_plan_of_another_width_class_is_refused(cuda):
+    indptr, indices = random_csr(**GRAPHS["dense"])
+    n = len(indptr) - 1
+    plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 16)
+    with pytest.raises(capi.EppError):
+        capi.spmm_segments(torch.zeros(n, 64, device=cuda), t(indices, cuda), plan)
+
+
+def test_result_overwrites_and_is_repeatable(cuda):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    out = torch.full((n, 16), 7.0, device=cuda)
+    a, want, _ = forward_case(cuda, indptr, indices, 16, out=out)
+    assert_close(a, want, 2e-5, 2e-6, what="first call into a dirty buffer")
+    b, _, _ = forward_case(cuda, indptr, indices, 16, out=out)
+    assert_close(b, want, 2e-5, 2e-6, what="second call into the previous result")
+
+
+@pytest.mark.parametrize("dim,left,right", [(8, 8, 0), (8, 4, 4), (22, 2, 0), (5, 3, 1), (7, 1, 0), (64, 64, 64)])
+def test_result_lands_in_a_column_block(cuda, dim, left, right):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    wide = torch.full((n, left + dim + right), 7.0, device=cuda)
+    got, want, _ = forward_case(cuda, indptr, indices, dim, out=wide[:, left:left + dim])
+    assert_close(got, want, 2e-5, 2e-6, what="planned forward column block")
+    full = wide.cpu().numpy()
+    assert (full[:, :left] == 7.0).all() and (full[:, left + dim:] == 7.0).all()
+
+
+def make_path(indptr, indices, ratio, layers, part_size, back_size, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    train = rng.random(len(indptr) - 1) < ratio
+    path, _ = O.prepare_execution_path(indptr, indices, train, layers, part_size, [back_size] * layers)
+    return path
+
+
+@pytest.mark.parametrize("dim", [1, 4, 16, 22, 64, 128, 150])
+@pytest.mark.parametrize("ratio", [0.0, 0.02, 0.15, 1.0])
+def test_backward_over_the_compacted_path(cuda, dim, ratio):
+    """Plan from the compacted row ids; rows off the path come back zero."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    d_out = rng.standard_normal((n, dim)).astype(np.float32)
+    src = padded_rows(d_out * deg[:, None], cuda, 8)
+    for conv in make_path(indptr, indices, ratio, 2, 6, 8, seed=dim + 1):
+        valid = conv["valid_len"]
+        ids = t(conv["id"], cuda)
+        plan = capi.SegmentPlan.from_ids(ids, valid, n, dim)
+        edges = t(conv["edgeList"], cuda)
+        out = torch.full((n, dim), 5.0, device=cuda)
+        capi.spmm_segments(src, edges, plan, t(deg, cuda), out=out)
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, d_out,
+                                         conv["numParts"])
+        got = out.cpu().numpy()
+        assert_close(got, want, 2e-5, 2e-6, what=f"planned backward dim {dim} ratio {ratio}")
+        assert np.all(got[conv["node_degs"] == 0] == 0), "rows off the path must come back zero"
+        assert plan.info["nonempty_rows"] == int((conv["node_degs"] > 0).sum())
+
+
+@pytest.mark.parametrize("dim", [16, 22])
+def test_agrees_with_the_group_kernel_on_rmat(cuda, dim):
+    """Both kernels on a power-law graph with hub rows of tens of thousands of edges."""
+    from eppgcn_b200 import graphs
+    g = graphs.make_graph("rmat16", 0)
+    n, e = g.num_nodes, g.num_edges
+    deg = degrees_of(g.indptr)
+    pp, p2n = O.build_part(max(e // n, 1), g.indptr)
+    gen = torch.Generator(device=cuda).manual_seed(dim)
+    ld = (dim + 7) // 8 * 8
+    src = torch.randn(n, ld, device=cuda, generator=gen)[:, :dim]
+    row, col, d = t(g.indptr, cuda), t(g.indices, cuda), t(deg, cuda)
+    a = capi.spmm_forward(src, row, col, d, t(pp, cuda), t(p2n, cuda), e // n, prescaled=True)
+    plan = capi.SegmentPlan.from_csr(row, e, dim)
+    b = capi.spmm_segments(src, col, plan, d)
+    c = capi.spmm_segments(src, col, plan, d, hub_rows=1024)
+    scale = a.abs().max().item()
+    assert torch.allclose(a, b, rtol=2e-5, atol=2e-6 * scale)
+    assert torch.allclose(a, c, rtol=2e-5, atol=2e-6 * scale)
+
+
+@pytest.mark.parametrize("dim", [1, 3, 5, 7, 21])
+def test_group_kernel_writes_the_last_column_of_an_odd_row_into_an_aligned_view(cuda, dim):
+    """Odd row width, source rows padded to 16 bytes, and a result view whose
+    stride and base allow 8- or 16-byte stores: the last column has no partner
+    in a two-float store and must still be written, forward and backward."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    pp, p2n = O.build_part(6, indptr)
+    src = padded_rows(feat, cuda, 4, poison=False)
+    for stride in ((dim + 1) // 2 * 2, (dim + 3) // 4 * 4 + 4):
+        wide = torch.full((n, stride), 7.0, device=cuda)
+        capi.spmm_forward(src, t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda), t(p2n, cuda), 6,
+                          out=wide[:, :dim])
+        assert_close(wide[:, :dim].cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat),
+                     what=f"forward dim {dim} stride {stride}")
+        conv = make_path(indptr, indices, 0.2, 1, 6, 8, seed=dim)[0]
+        wide.fill_(7.0)
+        capi.spmm_backward_compacted(src, t(conv["id"], cuda), t(conv["partPointer"], cuda),
+                                     t(conv["edgeList"], cuda), t(deg, cuda), conv["numParts"], 8,
+                                     out=wide[:, :dim])
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, feat,
+                                         conv["numParts"])
+        assert_close(wide[:, :dim].cpu().numpy(), want, what=f"backward dim {dim} stride {stride}")
+        assert (wide[:, dim:].cpu().numpy() == 7.0).all()

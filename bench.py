@@ -227,8 +227,8 @@ def run_gpu(args):
     spec0 = graphs.WORKLOADS[args.workload]
     if world > 1 or spec0.get("draw") == "device":
         # several ranks, or a workload that is drawn on the GPU: the row-partitioned driver (also at one rank)
-        from eppgcn_b200 import dist as epp_dist
-        return epp_dist.run_bench(args, rank, world, dev)
+        import bench_multi
+        return bench_multi.run_bench(args, rank, world, dev)
 
     spec = graphs.WORKLOADS[args.workload]
     t0 = time.perf_counter()

@@ -32,7 +32,7 @@ SIGNATURES = {
     "eppgcn_segment_plan_from_ids": (_I, [_P, _P, _SZ, _P, _LL, _I, _I, _P]),
     "eppgcn_segment_plan_destroy": (None, [_P]),
     "eppgcn_segment_plan_info": (_I, [_P, _P]),
-    "eppgcn_spmm_segments": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _I, _I, _P]),
+    "eppgcn_spmm_segments": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _I, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
@@ -219,7 +219,7 @@ class SegmentPlan:
             self._handle = None
 
 
-def spmm_segments(src, col_idx, plan, row_scale=None, out=None, hub_rows=0):
+def spmm_segments(src, col_idx, plan, row_scale=None, out=None):
     """``out[r] = row_scale[r] * sum_e src[col_idx[e]]`` over the rows of ``plan``;
     ``src`` rows already carry their source-side factor and may be padded."""
     n = plan.info["rows"]
@@ -230,7 +230,7 @@ def spmm_segments(src, col_idx, plan, row_scale=None, out=None, hub_rows=0):
     check(lib().eppgcn_spmm_segments(
         _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), ld,
         _dev(col_idx, torch.int32, "col_idx"), plan._handle,
-        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, int(hub_rows), _stream()))
+        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, _stream()))
     return out
 
 

@@ -6,7 +6,7 @@
 // whatever rows they belong to.  A sub-warp of LPR lanes owns one chunk, a
 // warp owns 32/LPR consecutive chunks ("a set").  Every sub-warp therefore has
 // the same number of edges, every load slot is used, and a chunk costs
-// 64/U rounds of U independent 16-byte row loads per lane -- the group kernel
+// eight rounds of eight independent 16-byte row loads per lane -- the group kernel
 // (spmm.cu) pays one round per tail batch of every short group instead.
 //
 // Row boundaries come from the plan: one 64-bit word per chunk with a bit at
@@ -24,10 +24,8 @@
 //
 // Source rows.  The kernel reads rows that already carry their source-side
 // factor (the update step, or the backward's packing step, folds it in), 16
-// bytes per lane and tile.  Optionally the first `hub_rows` rows of the source
-// matrix are copied into shared memory when a block starts and served from
-// there: with a producer that places the most referenced rows first, the share
-// of gathers that leave the SM shrinks by the hubs' share of the edges.
+// bytes per lane; a row of up to 16 / 32 / 64 / 128 columns is covered by 4 /
+// 8 / 16 / 32 lanes, wider rows take one launch per 128 columns.
 #include <mutex>
 #include <new>
 
@@ -58,13 +56,8 @@ constexpr int kPlanTile = 1024;       // chunks per block in the rank scan
 #ifndef EPP_SEG_MINB
 #define EPP_SEG_MINB 3
 #endif
-#ifndef EPP_HUB_THREADS
-#define EPP_HUB_THREADS 768
-#endif
 constexpr int kSegThreads = EPP_SEG_THREADS;
 constexpr int kSegMinBlocks = EPP_SEG_MINB;
-constexpr int kHubThreads = EPP_HUB_THREADS;
-constexpr int kMaxHubBytes = 200 * 1024;
 
 struct SegArgs {
   float *out;
@@ -80,166 +73,149 @@ struct SegArgs {
   int num_chunks;
   int dim;                        // columns handled by this launch
   int ovec;
-  int hub_rows;
 };
 
-// U column ids of one chunk starting at p (16-byte aligned when FULL).
-template <int U, bool FULL>
-__device__ __forceinline__ void load_ids(const int *p, int left, int (&c)[U]) {
-  if constexpr (FULL && U == 8) {
+// Eight column ids of one chunk starting at p (16-byte aligned); `left` edges
+// of the chunk remain, ids beyond them are not read.
+__device__ __forceinline__ void load_ids(const int *p, int left, int (&c)[8]) {
+  if (left >= 8) {
     const int4 a = __ldg(reinterpret_cast<const int4 *>(p));
     const int4 b = __ldg(reinterpret_cast<const int4 *>(p) + 1);
     c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w; c[4] = b.x; c[5] = b.y; c[6] = b.z; c[7] = b.w;
-  } else if constexpr (FULL && U == 4) {
-    const int4 a = __ldg(reinterpret_cast<const int4 *>(p));
-    c[0] = a.x; c[1] = a.y; c[2] = a.z; c[3] = a.w;
-  } else if constexpr (FULL && U == 2) {
-    const int2 a = __ldg(reinterpret_cast<const int2 *>(p));
-    c[0] = a.x; c[1] = a.y;
   } else {
 #pragma unroll
-    for (int u = 0; u < U; ++u) c[u] = (FULL || u < left) ? __ldg(p + u) : 0;
+    for (int u = 0; u < 8; ++u) c[u] = u < left ? __ldg(p + u) : 0;
   }
 }
 
-// Issues the row loads of one batch; nothing is consumed here, so all
-// U*T 16-byte loads of the lane are in flight together.
-template <int LPR, int T, int U, bool FULL, bool HUB>
-__device__ __forceinline__ void gather_rows(const int (&c)[U], int left, unsigned tiles, const char *glane,
-                                            unsigned ld_bytes, const float *hlane, int hub_ld, int hub_rows,
-                                            float4 (&v)[U][T]) {
-  constexpr unsigned kTileBytes = 16u * LPR;
-#pragma unroll
-  for (int u = 0; u < U; ++u) {
-    if (FULL || u < left) {
-      const unsigned cu = static_cast<unsigned>(c[u]);
-      if (HUB && cu < static_cast<unsigned>(hub_rows)) {
-        const float *p = hlane + cu * hub_ld;
-#pragma unroll
-        for (int k = 0; k < T; ++k)
-          v[u][k] = ((tiles >> k) & 1u) ? *reinterpret_cast<const float4 *>(p + k * 4 * LPR)
-                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-      } else {
-        const char *p = glane + static_cast<unsigned long long>(cu) * ld_bytes;
-#pragma unroll
-        for (int k = 0; k < T; ++k)
-          v[u][k] = ((tiles >> k) & 1u) ? __ldg(reinterpret_cast<const float4 *>(p + k * kTileBytes))
-                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < T; ++k) v[u][k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-  }
+__device__ __forceinline__ void add4(float (&acc)[4], const float4 &v) {
+  acc[0] += v.x; acc[1] += v.y; acc[2] += v.z; acc[3] += v.w;
 }
 
-template <int T>
-__device__ __forceinline__ void add4(float (&acc)[T][4], const float4 (&v)[T]) {
-#pragma unroll
-  for (int k = 0; k < T; ++k) {
-    acc[k][0] += v[k].x; acc[k][1] += v[k].y; acc[k][2] += v[k].z; acc[k][3] += v[k].w;
-  }
+// Row id and destination-side factor of the row with rank `rank`.
+__device__ __forceinline__ void row_of_rank(const SegArgs &a, int rank, int &row, float &scale) {
+  row = a.rows ? __ldg(a.rows + rank) : rank;
+  scale = a.row_scale ? __ldg(a.row_scale + row) : 1.f;
 }
 
-// Writes one finished (or partial, when `atomic`) row sum: the lane's tiles,
-// times the destination-side factor of the row.
-template <int LPR, int T>
-__device__ __forceinline__ void flush_row(const SegArgs &a, int rank, const float (&acc)[T][4], bool atomic,
-                                          int fcol, unsigned tiles) {
-  if (!tiles) return;
-  const int row = a.rows ? __ldg(a.rows + rank) : rank;
-  const float s = a.row_scale ? __ldg(a.row_scale + row) : 1.f;
-  float *dst = a.out + static_cast<long long>(row) * a.out_ld + fcol;
-#pragma unroll
-  for (int k = 0; k < T; ++k) {
-    if ((tiles >> k) & 1u) {
-      const int n = min(4, a.dim - (fcol + k * 4 * LPR));
-      const float val[4] = {acc[k][0] * s, acc[k][1] * s, acc[k][2] * s, acc[k][3] * s};
-      if (atomic) add_row<4>(dst + k * 4 * LPR, val, n, a.ovec);
-      else store_row<4>(dst + k * 4 * LPR, val, n, a.ovec);
-    }
-  }
+// The lane's four columns of a row sum, times `scale`, to `dst` (n <= 4 of
+// them exist): a plain store, or an atomic add for a piece of a row that other
+// warps add to as well.
+template <int OV>
+__device__ __forceinline__ void put4(float *dst, const float (&acc)[4], float scale, int n, bool atomic) {
+  const float val[4] = {acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale};
+  if (atomic) add_row<4>(dst, val, n, OV);
+  else store_row<4>(dst, val, n, OV);
 }
 
-// The 64 (or, in the last set of the list, fewer) edges of one chunk.  `bits`
-// holds the row starts of the chunk without bit 0 (a start at the first edge
-// closes nothing).  On return `acc` is the sum of the chunk's last row piece,
-// `head` the sum of the piece before the first start (only meaningful when the
-// chunk began inside a row), `cur` the rank of the last piece's row and
-// `nseen` the number of starts met, the one at edge 0 included.
-template <int LPR, int T, int U, bool FULL, bool HUB>
-__device__ __forceinline__ void run_chunk(const SegArgs &a, const int *cp, int len, int maxlen,
-                                          unsigned long long bits, unsigned tiles, const char *glane,
-                                          unsigned ld_bytes, const float *hlane, int fcol,
-                                          float (&acc)[T][4], float (&head)[T][4], int &cur, int &nseen) {
-  int c[U], cn[U];
-  load_ids<U, FULL>(cp, len, c);
-#pragma unroll
-  for (int u = 0; u < U; ++u) cn[u] = c[u];
-  const int trips = FULL ? kChunk : maxlen;
+// The 64 (or, at the end of the list, fewer) edges of one chunk.  `bits` holds
+// the row starts of the chunk without bit 0 (a start at the first edge closes
+// nothing).  On return `acc` is the sum of the chunk's last piece, `head` the
+// sum of the piece in front of the chunk's first start when the chunk began
+// inside a row (`nseen` == 0 on entry), `cur` the rank of the last piece's row
+// and `nseen` the number of starts met, the one at edge 0 included.
+//
+// A batch is eight edges.  Where a batch holds row starts, the per-edge step is
+// branch-free: the running sum is parked in the lane's shared-memory slots
+// (`stage`, slot i at stage[i * kSegThreads]) under a predicate and the sum
+// restarts from the edge's row.  The parked sums are written out afterwards in
+// a loop whose trip count is the same for the whole warp, so rows that close
+// at different edges in different sub-warps are stored by the same
+// instructions.  The row ids and factors of the rows that close in a batch are
+// asked for together with the batch's source rows.
+template <int LPR, int OV>
+__device__ __forceinline__ void run_chunk(const SegArgs &a, const int *cp, int len, int trips,
+                                          unsigned long long bits, bool has_cols, const char *glane,
+                                          unsigned ld_bytes, float *out_lane, int n, int sub, int sl,
+                                          unsigned sub_mask, float4 *stage, float (&acc)[4], float (&head)[4],
+                                          int &cur, int &nseen) {
+  constexpr int U = 8;                             // edges per batch: U row loads in flight per lane
+  int c[U];
+  load_ids(cp, len, c);
 #pragma unroll 1
   for (int b = 0; b < trips; b += U) {
-    float4 v[U][T];
+    float4 v[U];
     const int left = len - b;
-    gather_rows<LPR, T, U, FULL, HUB>(c, left, tiles, glane, ld_bytes, hlane, static_cast<int>(a.src_ld),
-                                      a.hub_rows, v);
-    if (b + U < kChunk) load_ids<U, FULL>(cp + b + U, left - U, cn);   // ids of the next batch, behind the gathers
-    const unsigned bb = static_cast<unsigned>(bits >> b) & ((1u << U) - 1u);
-    if (bb == 0u) {
+    // Nothing is consumed in this loop, so U loads are in flight.  Ids past the end of the list are
+    // 0 (row 0 is read and not added); lanes without columns read column 0 and never store.
 #pragma unroll
-      for (int u = 0; u < U; ++u) add4<T>(acc, v[u]);
+    for (int u = 0; u < U; ++u)
+      v[u] = __ldg(reinterpret_cast<const float4 *>(
+          glane + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes));
+    if (b + U < kChunk) load_ids(cp + b + U, left - U, c);      // ids of the next batch, behind the gathers
+#ifdef EPP_SEG_NOCLOSE
+    const unsigned bb = 0u;                        // timing experiment: rows are never closed inside a chunk
+#else
+    const unsigned bb = static_cast<unsigned>(bits >> b) & ((1u << U) - 1u);
+#endif
+    // One decision for the whole warp: the branch below holds warp-wide votes and shuffles.
+    if (!__any_sync(kFull, bb != 0u || left < U)) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) add4(acc, v[u]);
     } else {
+      // The rows that close in this batch have ranks cur, cur+1, ...: lane j of the sub-warp asks
+      // for the row id and factor of the j-th one (and of the (j+LPR)-th when a batch can close more
+      // rows than the sub-warp has lanes).
+      const int ncl = __popc(bb);
+      int rw0 = 0, rw1 = 0;
+      float sc0 = 1.f, sc1 = 1.f;
+      if (sl < ncl) row_of_rank(a, cur + sl, rw0, sc0);
+      if (LPR < U && sl + LPR < ncl) row_of_rank(a, cur + sl + LPR, rw1, sc1);
+      if (left < U) {                              // end of the list: edges that do not exist add nothing
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          if (u >= left) v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+      int cnt = 0;
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        if ((bb >> u) & 1u) {                      // edge b+u starts a row: close the running piece
-          if (nseen == 0) {
-#pragma unroll
-            for (int k = 0; k < T; ++k)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) head[k][i] = acc[k][i];
-          } else {
-            flush_row<LPR, T>(a, cur, acc, false, fcol, tiles);
-          }
-#pragma unroll
-          for (int k = 0; k < T; ++k)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[k][i] = 0.f;
-          ++cur;
-          ++nseen;
-        }
-        add4<T>(acc, v[u]);
+        const bool p = ((bb >> u) & 1u) != 0u;     // edge b+u starts a row: park the running sum, restart
+        if (p) stage[cnt * kSegThreads] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        cnt += p ? 1 : 0;
+        acc[0] = (p ? 0.f : acc[0]) + v[u].x;
+        acc[1] = (p ? 0.f : acc[1]) + v[u].y;
+        acc[2] = (p ? 0.f : acc[2]) + v[u].z;
+        acc[3] = (p ? 0.f : acc[3]) + v[u].w;
       }
-    }
+      const int most = __reduce_max_sync(kFull, ncl);
+#pragma unroll 1
+      for (int i = 0; i < most; ++i) {
+        if (i < ncl) {
+          const float4 s4 = stage[i * kSegThreads];
+          const int from = (sub * LPR) + (i & (LPR - 1));
+          const bool second = LPR < U && i >= LPR;
+          const int row = __shfl_sync(sub_mask, second ? rw1 : rw0, from);
+          const float scale = __shfl_sync(sub_mask, second ? sc1 : sc0, from);
+          const float piece[4] = {s4.x, s4.y, s4.z, s4.w};
+          if (i == 0 && nseen == 0) {              // the piece in front of the chunk's first start
 #pragma unroll
-    for (int u = 0; u < U; ++u) c[u] = cn[u];
+            for (int q = 0; q < 4; ++q) head[q] = piece[q];
+          } else if (has_cols) {
+            put4<OV>(out_lane + static_cast<long long>(row) * a.out_ld, piece, scale, n, false);
+          }
+        }
+      }
+      cur += ncl;
+      nseen += ncl;
+    }
   }
 }
 
-template <int LPR, int T, bool HUB>
-__global__ void __launch_bounds__(HUB ? kHubThreads : kSegThreads, HUB ? 1 : kSegMinBlocks)
-segment_spmm_kernel(const SegArgs a) {
+template <int LPR, int OV>
+__global__ void __launch_bounds__(kSegThreads, kSegMinBlocks) segment_spmm_kernel(const SegArgs a) {
   constexpr int G = kWarp / LPR;               // chunks per set
-  constexpr int U = T >= 8 ? 1 : 8 / T;        // edges per batch: U*T row loads in flight per lane
-  extern __shared__ __align__(16) float s_hub[];
+  __shared__ float4 s_stage[8 * kSegThreads];  // eight parked row sums per lane, slot-major
   const int lane = threadIdx.x & 31;
   const int sub = lane / LPR;
   const int sl = lane % LPR;
   const int fcol = sl * 4;
-  unsigned tiles = 0;
-#pragma unroll
-  for (int k = 0; k < T; ++k)
-    if (fcol + k * 4 * LPR < a.dim) tiles |= 1u << k;
-
-  if (HUB) {                                   // the hub rows, once per block
-    const int n4 = static_cast<int>(a.hub_rows * a.src_ld / 4);
-    const float4 *g4 = reinterpret_cast<const float4 *>(a.src);
-    float4 *s4 = reinterpret_cast<float4 *>(s_hub);
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) s4[i] = __ldg(g4 + i);
-    __syncthreads();
-  }
-  const char *glane = reinterpret_cast<const char *>(a.src + fcol);
-  const float *hlane = s_hub + fcol;
+  const bool has_cols = fcol < a.dim;
+  const int n = min(4, a.dim - fcol);          // columns of this lane that exist
+  const unsigned sub_mask = (LPR == 32 ? kFull : ((1u << LPR) - 1u)) << (sub * LPR);
+  float4 *stage = s_stage + threadIdx.x;
+  const char *glane = reinterpret_cast<const char *>(a.src + (has_cols ? fcol : 0));
   const unsigned ld_bytes = static_cast<unsigned>(a.src_ld) * 4u;
+  float *const out_lane = a.out + fcol;
 
   const int wpb = blockDim.x >> 5;
   const long long stride = static_cast<long long>(gridDim.x) * wpb;
@@ -267,72 +243,65 @@ segment_spmm_kernel(const SegArgs a) {
     const bool valid = k < a.num_chunks;
     const long long e0 = k * kChunk;
     const int len = valid ? static_cast<int>(min(static_cast<long long>(kChunk), a.num_edges - e0)) : 0;
-    const bool full = (set + 1) * G * kChunk <= a.num_edges;      // warp-uniform
     const bool open_head = valid && (m & 1ull) == 0ull;           // the chunk begins inside a row
-    const int head_rank = cur;
+    int head_row = 0;
+    float head_scale = 1.f;
+    if (open_head) row_of_rank(a, cur, head_row, head_scale);     // needed after the edge loop; asked for now
 
-    float acc[T][4], head[T][4];
-#pragma unroll
-    for (int k2 = 0; k2 < T; ++k2)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) { acc[k2][i] = 0.f; head[k2][i] = 0.f; }
+    float acc[4] = {0.f, 0.f, 0.f, 0.f}, head[4] = {0.f, 0.f, 0.f, 0.f};
     int nseen = static_cast<int>(m & 1ull);
-    const unsigned long long bits = m & ~1ull;
-    const int *cp = a.col + e0;
-    if (full) {
-      run_chunk<LPR, T, U, true, HUB>(a, cp, kChunk, kChunk, bits, tiles, glane, ld_bytes, hlane, fcol,
-                                      acc, head, cur, nseen);
-    } else {
-      const int maxlen = __reduce_max_sync(kFull, len);
-      run_chunk<LPR, T, U, false, HUB>(a, cp, len, maxlen, bits, tiles, glane, ld_bytes, hlane, fcol,
-                                       acc, head, cur, nseen);
-    }
+    const int trips = (set + 1) * G * kChunk <= a.num_edges ? kChunk : __reduce_max_sync(kFull, len);
+    run_chunk<LPR, OV>(a, a.col + e0, len, trips, m & ~1ull, has_cols, glane, ld_bytes, out_lane, n, sub, sl,
+                       sub_mask, stage, acc, head, cur, nseen);
 
     // -- open ends: hand the last piece of every chunk to the sub-warp on its right ------------------
+    // `acc` is the carry this sub-warp sends on, with the row it belongs to and that row's factor;
+    // carry_ext: the piece began before this set.
     const bool has_start = nseen > 0;
-    // `acc` now is the carry this sub-warp sends on; carry_ext: the piece began before this set
-    int carry_rank = cur;
+    int carry_row = head_row;
+    float carry_scale = head_scale;
+    if (has_start && len > 0) row_of_rank(a, cur, carry_row, carry_scale);
     bool carry_ext = !has_start;               // a chunk without a start passes on what it received (none yet)
     bool carry_valid = len > 0;
-    if (sub == 0 && has_start && open_head) flush_row<LPR, T>(a, head_rank, head, true, fcol, tiles);
-#pragma unroll
+    if (sub == 0 && has_start && open_head && has_cols)
+      put4<OV>(out_lane + static_cast<long long>(head_row) * a.out_ld, head, head_scale, n, true);
+#pragma unroll 1
     for (int j = 1; j < G; ++j) {
-      float inc[T][4];
+      float inc[4];
 #pragma unroll
-      for (int k2 = 0; k2 < T; ++k2)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) inc[k2][i] = __shfl_up_sync(kFull, acc[k2][i], LPR);
-      const int inc_rank = __shfl_up_sync(kFull, carry_rank, LPR);
+      for (int i = 0; i < 4; ++i) inc[i] = __shfl_up_sync(kFull, acc[i], LPR);
+      const int inc_row = __shfl_up_sync(kFull, carry_row, LPR);
+      const float inc_scale = __shfl_up_sync(kFull, carry_scale, LPR);
       const int inc_flags = __shfl_up_sync(kFull, (carry_ext ? 1 : 0) | (carry_valid ? 2 : 0), LPR);
       const bool inc_ext = (inc_flags & 1) != 0, inc_valid = (inc_flags & 2) != 0;
       if (sub == j) {
         if (len == 0) {                        // past the end of the list: pass the carry through
 #pragma unroll
-          for (int k2 = 0; k2 < T; ++k2)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[k2][i] = inc[k2][i];
-          carry_rank = inc_rank; carry_ext = inc_ext; carry_valid = inc_valid;
+          for (int i = 0; i < 4; ++i) acc[i] = inc[i];
+          carry_row = inc_row; carry_scale = inc_scale; carry_ext = inc_ext; carry_valid = inc_valid;
         } else if (has_start) {
-          if (open_head) {                     // the row that ends in this chunk: earlier pieces + head
+          // either the row that ends in this chunk (earlier pieces + head), or, when the chunk begins
+          // with a start, the row that ended exactly at the chunk boundary
+          if (open_head) {
 #pragma unroll
-            for (int k2 = 0; k2 < T; ++k2)
-#pragma unroll
-              for (int i = 0; i < 4; ++i) head[k2][i] += inc_valid ? inc[k2][i] : 0.f;
-            flush_row<LPR, T>(a, head_rank, head, inc_ext || !inc_valid, fcol, tiles);
-          } else if (inc_valid) {              // the row ended exactly at the chunk boundary
-            flush_row<LPR, T>(a, inc_rank, inc, inc_ext, fcol, tiles);
+            for (int i = 0; i < 4; ++i) inc[i] = head[i] + (inc_valid ? inc[i] : 0.f);
           }
+          const int row = open_head ? head_row : inc_row;
+          const float scale = open_head ? head_scale : inc_scale;
+          const bool atomic = open_head ? (inc_ext || !inc_valid) : inc_ext;
+          if ((open_head || inc_valid) && has_cols)
+            put4<OV>(out_lane + static_cast<long long>(row) * a.out_ld, inc, scale, n, atomic);
         } else {                               // the whole chunk lies inside one row
 #pragma unroll
-          for (int k2 = 0; k2 < T; ++k2)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[k2][i] += inc_valid ? inc[k2][i] : 0.f;
-          carry_rank = inc_valid ? inc_rank : head_rank;
+          for (int i = 0; i < 4; ++i) acc[i] += inc_valid ? inc[i] : 0.f;
+          if (inc_valid) { carry_row = inc_row; carry_scale = inc_scale; }
           carry_ext = inc_valid ? inc_ext : true;
         }
       }
     }
-    if (sub == G - 1 && carry_valid) flush_row<LPR, T>(a, carry_rank, acc, carry_ext || !next_starts, fcol, tiles);
+    if (sub == G - 1 && carry_valid && has_cols)
+      put4<OV>(out_lane + static_cast<long long>(carry_row) * a.out_ld, acc, carry_scale, n,
+               carry_ext || !next_starts);
   }
 }
 
@@ -515,10 +484,11 @@ __global__ void __launch_bounds__(256) plan_rows_ids_kernel(const int *__restric
   if ((mask[e >> 6] >> (e & 63)) & 1ull) rows[rank_of_start(mask, first_rank, e)] = __ldg(ids + e);
 }
 
-int lanes_for_dim(int dim) {            // lanes per row of the kernel shape that serves `dim` columns
-  if (dim <= 32) return 4;
-  if (dim <= 64) return 8;
-  return 16;
+int lanes_for_dim(int dim) {            // lanes per row: four columns per lane, at most 128 columns per launch
+  if (dim <= 16) return 4;
+  if (dim <= 32) return 8;
+  if (dim <= 64) return 16;
+  return 32;
 }
 
 size_t round256(size_t b) { return (b + 255) / 256 * 256; }
@@ -603,34 +573,33 @@ int plan_read_counts(eppgcn_segment_plan *p, bool from_csr, cudaStream_t s) {
   return EPP_OK;
 }
 
-template <int LPR, int T, bool HUB>
-int launch_segments(const SegArgs &a, int hub_bytes, cudaStream_t s) {
+template <int LPR, int OV>
+int launch_segments(const SegArgs &a, cudaStream_t s) {
   constexpr int G = kWarp / LPR;
-  static SmemOptIn memo;
   int num_sms = 0;
   if (const int rc = device_sm_count(&num_sms); rc != EPP_OK) return rc;
-  const int threads = HUB ? kHubThreads : kSegThreads;
-  const int per_sm = HUB ? 1 : kSegMinBlocks;
-  if (HUB)
-    if (const int rc = smem_opt_in(memo, reinterpret_cast<const void *>(segment_spmm_kernel<LPR, T, HUB>), hub_bytes);
-        rc != EPP_OK)
-      return rc;
   const long long nsets = ceil_div_ll(a.num_chunks, G);
-  long long blocks = ceil_div_ll(nsets, threads / kWarp);
-  const long long cap = static_cast<long long>(num_sms) * per_sm;
+  long long blocks = ceil_div_ll(nsets, kSegThreads / kWarp);
+  const long long cap = static_cast<long long>(num_sms) * kSegMinBlocks;
   if (blocks > cap) blocks = cap;
-  segment_spmm_kernel<LPR, T, HUB><<<static_cast<unsigned>(blocks), threads, HUB ? hub_bytes : 0, s>>>(a);
+  segment_spmm_kernel<LPR, OV><<<static_cast<unsigned>(blocks), kSegThreads, 0, s>>>(a);
   EPP_CHECK_LAUNCH("segment_spmm_kernel");
   return EPP_OK;
 }
 
-// The plan fixes the lanes per row (its list of cleared rows belongs to that
-// set size); the columns of this launch pick the tiles per lane.
-template <bool HUB>
-int launch_by_width(const SegArgs &a, int lanes, int hub_bytes, cudaStream_t s) {
-  if (lanes == 4) return a.dim <= 16 ? launch_segments<4, 1, HUB>(a, hub_bytes, s) : launch_segments<4, 2, HUB>(a, hub_bytes, s);
-  if (lanes == 8) return a.dim <= 32 ? launch_segments<8, 1, HUB>(a, hub_bytes, s) : launch_segments<8, 2, HUB>(a, hub_bytes, s);
-  return a.dim <= 64 ? launch_segments<16, 1, HUB>(a, hub_bytes, s) : launch_segments<16, 2, HUB>(a, hub_bytes, s);
+template <int LPR>
+int launch_by_store(const SegArgs &a, cudaStream_t s) {
+  if (a.ovec == 4) return launch_segments<LPR, 4>(a, s);
+  if (a.ovec == 2) return launch_segments<LPR, 2>(a, s);
+  return launch_segments<LPR, 1>(a, s);
+}
+
+// The plan fixes the lanes per row: its list of cleared rows belongs to that set size.
+int launch_by_width(const SegArgs &a, int lanes, cudaStream_t s) {
+  if (lanes == 4) return launch_by_store<4>(a, s);
+  if (lanes == 8) return launch_by_store<8>(a, s);
+  if (lanes == 16) return launch_by_store<16>(a, s);
+  return launch_by_store<32>(a, s);
 }
 
 }  // namespace
@@ -708,17 +677,17 @@ EPP_EXPORT int eppgcn_segment_plan_info(const eppgcn_segment_plan *plan, long lo
 
 EPP_EXPORT int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long long src_ld,
                                     const int *col_idx, const eppgcn_segment_plan *plan, const float *row_scale,
-                                    int dim, int hub_rows, void *stream) {
+                                    int dim, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   EPP_REQUIRE(plan, "null plan");
-  EPP_REQUIRE(dim >= 1 && hub_rows >= 0, "dim < 1 or negative hub_rows");
+  EPP_REQUIRE(dim >= 1, "dim < 1");
   EPP_REQUIRE(out_ld == 0 || out_ld >= dim, "out_ld must be 0 or >= dim");
   const int n = plan->num_rows;
   if (n == 0) return EPP_OK;
   EPP_REQUIRE(out, "null pointer");
   if (out_ld == 0) out_ld = dim;
   EPP_REQUIRE(kWarp / lanes_for_dim(dim > 128 ? 128 : dim) == plan->groups,
-              "the plan was prepared for another row width class (<= 32, <= 64, wider)");
+              "the plan was prepared for another row width class (<= 16, <= 32, <= 64, wider)");
   int ovec = 1;
   if (out_ld % 4 == 0 && aligned(out, 16)) ovec = 4;
   else if (out_ld % 2 == 0 && aligned(out, 8)) ovec = 2;
@@ -742,17 +711,14 @@ EPP_EXPORT int eppgcn_spmm_segments(float *out, long long out_ld, const float *s
   EPP_REQUIRE(src_ld % 4 == 0 && src_ld >= (dim + 3) / 4 * 4 && src_ld <= 0x3fffffffLL && aligned(src, 16),
               "source rows must be 16-byte aligned and padded to a multiple of 4 floats");
   EPP_REQUIRE(aligned(col_idx, 16), "col_idx must be 16-byte aligned");
-  const long long hub_bytes = static_cast<long long>(hub_rows) * src_ld * 4;
-  EPP_REQUIRE(hub_bytes <= kMaxHubBytes, "hub rows exceed the shared memory of an SM");
   for (int col0 = 0; col0 < dim; col0 += 128) {          // one launch unless the row is wider than 128
     SegArgs a{};
     a.out = out + col0; a.out_ld = out_ld; a.src = src + col0; a.src_ld = src_ld; a.col = col_idx;
     a.mask = plan->mask; a.first_rank = plan->first_rank; a.rows = plan->identity ? nullptr : plan->rows;
     a.row_scale = row_scale; a.num_edges = plan->num_edges; a.num_chunks = plan->num_chunks;
-    a.dim = dim - col0 < 128 ? dim - col0 : 128; a.ovec = ovec; a.hub_rows = hub_rows;
+    a.dim = dim - col0 < 128 ? dim - col0 : 128; a.ovec = ovec;
     const int lanes = kWarp / plan->groups;
-    const int rc = (hub_rows > 0 && dim <= 128) ? launch_by_width<true>(a, lanes, static_cast<int>(hub_bytes), s)
-                                                : launch_by_width<false>(a, lanes, 0, s);
+    const int rc = launch_by_width(a, lanes, s);
     if (rc != EPP_OK) return rc;
   }
   return EPP_OK;

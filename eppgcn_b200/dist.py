@@ -719,236 +719,3 @@ class DistHotPath:
         return self.capi.spmm_backward_compacted(buf, p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
                                                  self.back_size, out=out_local, deg_row=self.deg_row,
                                                  num_rows=self.shard.num_rows)
-
-
-def run_bench(args, rank: int, world: int, dev):
-    """Multi-GPU arm of bench.py: the forward and backward aggregations of every
-    layer, row-partitioned, each preceded by the exchange of its source rows.
-    Strong scaling: the graph is fixed and split over the ranks.  Workloads whose
-    ``WORKLOADS`` entry is too large for the host generator are drawn on the GPU
-    (every rank draws the same graph from the same seed)."""
-    from eppgcn_b200 import graphs
-    import bench as B
-    if not dist.is_initialized():
-        if "MASTER_ADDR" in os.environ:
-            dist.init_process_group("nccl", device_id=dev)
-        else:       # plain `python bench.py` with a device-drawn workload: a group of one
-            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1,
-                                    device_id=dev)
-    spec = graphs.WORKLOADS[args.workload]
-    device_drawn = spec.get("draw") == "device"
-    t0 = time.perf_counter()
-    if device_drawn:
-        ds = graphs.DeviceWorkload(args.workload, args.seed, dev)
-    else:
-        if rank == 0:
-            ds = graphs.load_workload(args.workload, args.seed)      # generates and caches the graph once per box
-        dist.barrier()
-        if rank != 0:
-            ds = graphs.load_workload(args.workload, args.seed)
-    n, e, L = ds.num_nodes, ds.num_edges, ds.num_layers
-    dims = [spec["hidden"]] * (L - 1) + [spec["classes"]]
-    mode = getattr(args, "exchange", "balanced")
-    if device_drawn and mode not in ("balanced", "balanced_halo"):
-        mode = "balanced"
-    halo = mode in ("halo", "balanced_halo")
-    chunks = getattr(args, "chunks", 0)
-    if chunks <= 0:           # measured on the 64/64/32-column workload: two 32-column buffers aggregate faster than one
-        chunks = 2 if min(dims) >= 32 and all(d % 8 == 0 for d in dims) else 1
-    hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=chunks,
-                     transport=getattr(args, "transport", "push"), overlap=getattr(args, "overlap", False))
-    dealt = mode == "balanced_halo"
-    if device_drawn:
-        ds.indptr = ds.indices = None           # the shard is all this rank needs from here on
-        torch.cuda.empty_cache()
-    setup_s = time.perf_counter() - t0
-    n_loc = hp.n_loc
-    gen = torch.Generator(device=dev).manual_seed(args.seed + rank)
-    # operations of one epoch: forward of every layer, then backward from the last layer down
-    ops = [("fwd", i, dims[i]) for i in range(L)] + [("bwd", i, dims[i]) for i in reversed(range(L))]
-    # forward inputs as the update step leaves them (padded rows), backward inputs as autograd does (dense)
-    if dealt:
-        # the producer of an input writes this rank's rows straight into the exchange buffers
-        local_in = [None] * len(ops)
-        staged = [hp.halo_inputs(kind, i, d) for kind, i, d in ops]
-        for views in staged:
-            for v in views:
-                v.normal_(generator=gen)
-    else:
-        local_in = [B.padded(n_loc, d, dev, gen) if kind == "fwd" else torch.randn(n_loc, d, device=dev, generator=gen)
-                    for kind, _, d in ops]
-        staged = [[x] for x in local_in]
-    outs = [torch.empty(n_loc, d, device=dev) for _, _, d in ops]
-    compact_bwd = "plan" in hp.path[0]
-    full = [None] * len(ops)
-    bufs = [None] * len(ops)
-    for k, (kind, i, d) in enumerate(ops):
-        if dealt:
-            continue                                  # the plans keep their own per-aggregation buffers
-        if halo:
-            bufs[k] = (hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).exchange(local_in[k])
-        elif kind == "bwd" and compact_bwd:
-            bufs[k] = hp.path[i]["plan"].exchange(local_in[k])
-        else:
-            full[k] = B.padded(hp.n, d, dev, gen) if kind == "fwd" else torch.empty(hp.n, d, device=dev)
-
-    def one(k):
-        kind, i, d = ops[k]
-        if kind == "bwd" and compact_bwd:
-            hp.backward_halo(i, local_in[k], outs[k])
-        elif halo:
-            hp.forward_halo(local_in[k], outs[k])
-        else:
-            hp.gather(full[k], local_in[k])
-            (hp.forward(full[k], outs[k]) if kind == "fwd" else hp.backward(i, full[k], outs[k]))
-
-    def local_only(k):
-        kind, i, d = ops[k]
-        if dealt:
-            return hp.halo_local(kind, i, outs[k])
-        if kind == "fwd":
-            if not halo:
-                return hp.forward(full[k], outs[k])
-            return hp.capi.spmm_forward(bufs[k], hp.row, hp.col_c, hp.deg, hp.pp, hp.p2n, hp.part_size,
-                                        out=outs[k], deg_row=hp.deg_row, prescaled=True)
-        if not compact_bwd:
-            return hp.backward(i, full[k], outs[k])
-        p = hp.path[i]
-        return hp.capi.spmm_backward_compacted(bufs[k], p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
-                                               hp.back_size, out=outs[k], deg_row=hp.deg_row, num_rows=n_loc)
-
-    def step():
-        for k in range(len(ops)):
-            one(k)
-
-    stream = torch.cuda.current_stream()
-    with B.ClockSampler(dev.index) as clocks:
-        for _ in range(max(args.warmup, 3)):
-            step()
-        torch.cuda.synchronize()
-        if hp.fabric is not None:
-            hp.fabric.check()
-        dist.barrier()
-        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        dist.barrier()
-        ev0.record(stream)
-        for _ in range(args.steps):
-            step()
-        ev1.record(stream)
-        torch.cuda.synchronize()
-        dist.barrier()
-        ms = torch.tensor([ev0.elapsed_time(ev1) / args.steps], device=dev)
-        # kernel-only share: the local SpMMs without the exchange
-        k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        k0.record(stream)
-        for _ in range(args.steps):
-            for k in range(len(ops)):
-                local_only(k)
-        k1.record(stream)
-        torch.cuda.synchronize()
-        kms = torch.tensor([k0.elapsed_time(k1) / args.steps], device=dev)
-    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    dist.all_reduce(kms, op=dist.ReduceOp.MAX)
-    if hp.fabric is not None:
-        hp.fabric.check()
-
-    # e2e: host buffers, every step stages this rank's rows in and its results out
-    host_in = [[torch.empty(x.shape, pin_memory=True).copy_(x) for x in views] for views in staged]
-    host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
-
-    def e2e_step():
-        for k in range(len(ops)):
-            for x, h in zip(staged[k], host_in[k]):
-                x.copy_(h, non_blocking=True)
-            one(k)
-            host_out[k].copy_(outs[k], non_blocking=True)
-
-    for _ in range(2):
-        e2e_step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    steps2 = max(3, min(args.steps, 10))
-    ev0.record(stream)
-    for _ in range(steps2):
-        e2e_step()
-    ev1.record(stream)
-    torch.cuda.synchronize()
-    e2e = torch.tensor([ev0.elapsed_time(ev1) / steps2], device=dev)
-    dist.all_reduce(e2e, op=dist.ReduceOp.MAX)
-    byts = torch.tensor([sum(x.numel() * 4 for views in staged for x in views), sum(o.numel() * 4 for o in outs)],
-                        device=dev, dtype=torch.int64)
-    dist.all_reduce(byts)
-    edges = torch.tensor([hp.shard.num_edges, n_loc], device=dev, dtype=torch.int64)
-    gathered = [torch.zeros_like(edges) for _ in range(world)]
-    dist.all_gather(gathered, edges)
-    if rank == 0:
-        peak, peak_src = B.measured_peak_gbs()
-        exchanged = [(bufs[k].size(0) if bufs[k] is not None else hp.n) for k in range(len(ops))]
-        if dealt:
-            exchanged = [(hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).num_remote for kind, i, _ in ops]
-        # compulsory bytes of rank 0's local aggregations (each input byte once, each output byte once)
-        e_loc = hp.shard.num_edges
-        algo = 0
-        for k, (kind, i, d) in enumerate(ops):
-            if kind == "fwd":
-                algo += 4 * e_loc + 4 * (n_loc + 1) + 4 * n_loc + 4 * d * min(exchanged[k] + n_loc, hp.n) + 4 * d * n_loc
-            else:
-                p = hp.path[i]
-                src_rows = min(exchanged[k] + n_loc, hp.n)
-                algo += (4 * p["valid"] + 4 * (p["parts"] + 1) + 4 * p["parts"] + 4 * d * src_rows
-                         + 4 * (p["rows"] + src_rows) + 4 * d * n_loc)
-        achieved = algo / (kms.item() * 1e-3) / 1e9
-        # this library's kernels per epoch: one SpMM per aggregation and column chunk (plus the zeroing kernel of a
-        # column block), and with the push transport one push per chunk and two barriers per aggregation
-        launches = 0
-        for kind, i, d in ops:
-            c = len((hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).buffers(d, hp.chunks)) if dealt else 1
-            launches += c * (2 if c > 1 else 1)
-            if dealt and hp.fabric is not None:
-                launches += c + 2
-        line = {
-            "metric": f"{L}-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms.item(), 4),
-            "unit": "ms/epoch", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": round(ms.item(), 4), "higher_is_better": False, "scaling": "strong",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: N={n}, E={e} directed incl. self loops, dims "
-                                   f"{'/'.join(str(d) for d in dims)}, train_ratio {spec['train_ratio']}, "
-                                   f"group size {hp.part_size}, backward part size {args.backsize}"
-                                   + (", graph drawn on the GPU" if device_drawn else ""),
-                       "seed": args.seed, "l2": "inputs exceed L2",
-                       "parallelism": f"rows{world}: "
-                                      + {"halo": "contiguous ranges, one NCCL all-to-all of the referenced source "
-                                                 "rows per aggregation",
-                                         "allgather": "contiguous ranges, one uneven NCCL row all-gather per aggregation",
-                                         "balanced_halo": "degree-dealt relabelling (equal rows and edges per "
-                                                          "rank); per aggregation only the referenced remote source "
-                                                          f"rows travel, in {hp.chunks} column chunk(s), "
-                                                          + ("gathered and stored into the readers' buffers over "
-                                                             "NVLink by one kernel of this library, flag barriers "
-                                                             "with bounded waits"
-                                                             + (", later chunks pushed on a side stream beside the "
-                                                                "aggregation" if getattr(args, "overlap", False) else "")
-                                                             if hp.fabric is not None else
-                                                             "by NCCL all-to-all"),
-                                         "balanced": "degree-dealt relabelling (equal rows and edges per rank), one "
-                                                     "NCCL all-gather per aggregation (source-mask rows only for "
-                                                     "the backward layers)"}[mode]},
-            "local_spmm_ms": round(kms.item(), 4), "exchange_ms": round(ms.item() - kms.item(), 4),
-            "shards": {"edges": [int(t[0]) for t in gathered], "rows": [int(t[1]) for t in gathered],
-                       "source_rows_per_aggregation": exchanged},
-            "roofline": {"bound": "hbm", "kernel": "rank 0's local SpMMs of one epoch, summed",
-                         "achieved": round(achieved, 1), "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                         "frac": round(achieved / peak, 4), "traffic": None, "algorithmic_bytes": int(algo),
-                         "note": "one GPU's compulsory bytes over its local kernel time; the per-kernel roofline "
-                                 "with ncu traffic is reported by the 1-GPU run of the default workload"},
-            "clocks": clocks.summary(),
-            "e2e": {"value": round(e2e.item(), 4), "unit": "ms/epoch", "h2d_bytes_per_step": int(byts[0]),
-                    "d2h_bytes_per_step": int(byts[1]),
-                    "what": "each rank stages its rows from pinned host memory, exchanges, aggregates, copies results back"},
-            "gpu_launches": launches * args.steps, "cpu_baseline": None,
-            "setup_s": round(setup_s, 2), "prep_s": round(hp.prep_s, 4),
-        }
-        print(json.dumps(line), flush=True)
-    dist.barrier()
-    dist.destroy_process_group()

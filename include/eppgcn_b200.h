@@ -109,7 +109,8 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
  * reference has no such object; it replaces the per-call zero-fill
  * (EPPGCN_kernel.cu:150, :562) and the per-group atomics (:289-293, :666-668):
  * the result is written once, rows are summed with atomics only where they
- * cross a warp's 512-edge span.
+ * cross the span of edges one warp works on (64 edges per group of lanes
+ * that covers a row).
  *
  *   out[r][:] = row_scale[r] * sum over edges e of row r:  src[col_idx[e]][:]
  *
@@ -122,7 +123,7 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
  * a few small kernels on `stream` and synchronises that stream once to read
  * two counts back.  The plan handle itself is a small host object, freed by
  * eppgcn_segment_plan_destroy.  `dim` selects the row-width class the plan
- * serves (<= 32 columns, <= 64, wider): eppgcn_spmm_segments rejects a plan
+ * serves (<= 16 columns, <= 32, <= 64, wider): eppgcn_spmm_segments rejects a plan
  * of another class.  eppgcn_segment_plan_info: out8 = {edges, rows, chunks,
  * chunks per warp, non-empty rows, rows cleared per call, row ids implicit,
  * whole result cleared per call}.
@@ -136,10 +137,6 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
  * col_idx   the edge list's source row per edge (positions into src),
  *           16-byte aligned.
  * row_scale destination-side factor per row id, or NULL for 1.
- * hub_rows  0, or a number of leading rows of src that every thread block
- *           copies into shared memory and serves from there
- *           (hub_rows * src_ld * 4 <= 200 KiB); pays when the producer of src
- *           places the most referenced rows first.
  */
 typedef struct eppgcn_segment_plan eppgcn_segment_plan;
 size_t eppgcn_segment_plan_bytes(long long num_edges, int num_rows);
@@ -153,7 +150,7 @@ void eppgcn_segment_plan_destroy(eppgcn_segment_plan *plan);
 int eppgcn_segment_plan_info(const eppgcn_segment_plan *plan, long long *out8);
 int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long long src_ld,
                          const int *col_idx, const eppgcn_segment_plan *plan, const float *row_scale,
-                         int dim, int hub_rows, void *stream);
+                         int dim, void *stream);
 
 /* ------------------------------------------------------------------------
  * Dense update of a layer with the source-side factor folded in.
@@ -255,15 +252,24 @@ int eppgcn_compact_mask(const int *edge_mask, const int *col_idx,
  * Limits and rules:
  *  - length <= 67,108,864 (2^26) edges; larger inputs return EPP_ERR_TOO_LARGE
  *    and must use eppgcn_compact_mask.
- *  - The array costs 131,328 bytes of device memory on every GPU that loads
- *    the library, for the life of the process.
- *  - The first call on a device looks up the array's device address (once per
- *    device, with that device current).  Make that first call outside any
- *    stream capture.
+ *  - The array costs 131,328 bytes of device memory on every GPU that uses
+ *    this library's kernels, for the life of the process.  With CUDA's default
+ *    lazy module loading it comes into being when the library's module is
+ *    first used on a device, not when the library file is loaded, and that
+ *    first use may allocate device memory implicitly.  Make one warm-up call
+ *    per device during start-up (any small input will do); calls after it
+ *    allocate nothing.
+ *  - The first call on a device also looks up the array's device address
+ *    (once per device, with that device current).  Make that first call
+ *    outside any stream capture -- the warm-up call above serves both ends.
  *  - All calls on a device share the one array.  Each call clears what it
  *    needs, so calls issued back to back on one stream are fine; two calls
  *    whose kernels can overlap on the GPU (different streams, no ordering)
  *    race on it and give undefined results.
+ *  - There is no second, wait-free attempt inside the call: when *status_dev
+ *    comes back as EPP_ERR_SCAN_TIMEOUT the outputs are void and the caller
+ *    repeats the compaction with eppgcn_compact_mask(mode = 1), which needs
+ *    caller scratch but never waits.
  */
 int eppgcn_compact_mask_static(const int *edge_mask, const int *col_idx,
                                int *out_id, int *out_edge, int length,

@@ -12,8 +12,8 @@ side.  The reference's own ``setup.py`` passes no architecture flag
 (EPPGCN/GCNConv/setup.py:15-16); sm_100 is selected here.
 
 Usage: ``python oracle/build_ref.py [reference_root]``; without an argument the
-root is ``$EPPGCN_REFERENCE_ROOT``, else where the build image mounts the
-reference tree.
+root is ``$EPPGCN_REFERENCE_ROOT``, else a checkout named ``reference`` beside
+this repository.
 """
 from __future__ import annotations
 
@@ -26,7 +26,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
 NAME = "eppgcn_reference"
 TARGET = os.path.join(OUT, NAME + sysconfig.get_config_var("EXT_SUFFIX"))
-DEFAULT_ROOT = os.environ.get("EPPGCN_REFERENCE_ROOT", "/root/reference")
+DEFAULT_ROOT = os.environ.get("EPPGCN_REFERENCE_ROOT") or os.path.normpath(os.path.join(HERE, "..", "..", "reference"))
 
 
 def build(reference_root: str = DEFAULT_ROOT, force: bool = False, verbose: bool = True) -> str | None:

@@ -34,7 +34,7 @@ def padded_rows(a, cuda, pad_to=4, poison=True):
     return full[:, :d]
 
 
-def forward_case(cuda, indptr, indices, dim, pad_to=4, hub_rows=0, seed=0, out=None):
+def forward_case(cuda, indptr, indices, dim, pad_to=4, seed=0, out=None):
     n = len(indptr) - 1
     rng = np.random.Generator(np.random.PCG64(seed))
     feat = rng.standard_normal((n, dim)).astype(np.float32)
@@ -42,7 +42,7 @@ def forward_case(cuda, indptr, indices, dim, pad_to=4, hub_rows=0, seed=0, out=N
     plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), dim)
     src = padded_rows(feat * deg[:, None], cuda, pad_to)
     col = t(indices, cuda) if len(indices) else torch.zeros(4, dtype=torch.int32, device=cuda)
-    got = capi.spmm_segments(src, col, plan, t(deg, cuda), out=out, hub_rows=hub_rows)
+    got = capi.spmm_segments(src, col, plan, t(deg, cuda), out=out)
     torch.cuda.synchronize()
     return got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), plan
 
@@ -68,8 +68,8 @@ def test_plan_counts(cuda):
     crossing = (deg > 0) & (indptr[:-1] // span != (indptr[1:] - 1) // span)
     assert info["cleared_rows"] == int((deg == 0).sum() + crossing.sum())
     assert info["implicit_row_ids"] == 0           # the graph has rows without edges
-    assert capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 64).info["chunks_per_warp"] == 4
-    assert capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 128).info["chunks_per_warp"] == 2
+    for dim, per_warp in ((22, 4), (64, 2), (128, 1), (300, 1)):
+        assert capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), dim).info["chunks_per_warp"] == per_warp
 
 
 def test_every_row_nonempty_uses_implicit_row_ids(cuda):
@@ -86,22 +86,6 @@ def test_every_row_nonempty_uses_implicit_row_ids(cuda):
     got, want, plan = forward_case(cuda, indptr, indices, 16)
     assert plan.info["implicit_row_ids"] == 1
     assert_close(got, want, 2e-5, 2e-6, what="implicit row ids")
-
-
-@pytest.mark.parametrize("dim,hub_rows", [(16, 64), (16, 700), (22, 100), (64, 128), (128, 50)])
-def test_hub_rows_from_shared_memory_give_the_same_result(cuda, dim, hub_rows):
-    indptr, indices = random_csr(**GRAPHS["hubs"])
-    got, want, _ = forward_case(cuda, indptr, indices, dim, pad_to=8, hub_rows=hub_rows)
-    assert_close(got, want, 2e-5, 2e-6, what=f"hub rows {hub_rows} dim {dim}")
-
-
-def test_hub_rows_beyond_shared_memory_are_refused(cuda):
-    indptr, indices = random_csr(**GRAPHS["dense"])
-    n = len(indptr) - 1
-    plan = capi.SegmentPlan.from_csr(t(indptr, cuda), len(indices), 128)
-    with pytest.raises(capi.EppError) as e:
-        capi.spmm_segments(torch.zeros(n, 128, device=cuda), t(indices, cuda), plan, hub_rows=401)
-    assert e.value.status == capi.EPP_ERR_BAD_ARG
 
 
 def test_plan_of_another_width_class_is_refused(cuda):
@@ -180,10 +164,8 @@ def test_agrees_with_the_group_kernel_on_rmat(cuda, dim):
     a = capi.spmm_forward(src, row, col, d, t(pp, cuda), t(p2n, cuda), e // n, prescaled=True)
     plan = capi.SegmentPlan.from_csr(row, e, dim)
     b = capi.spmm_segments(src, col, plan, d)
-    c = capi.spmm_segments(src, col, plan, d, hub_rows=1024)
     scale = a.abs().max().item()
     assert torch.allclose(a, b, rtol=2e-5, atol=2e-6 * scale)
-    assert torch.allclose(a, c, rtol=2e-5, atol=2e-6 * scale)
 
 
 @pytest.mark.parametrize("dim", [1, 3, 5, 7, 21])

@@ -42,6 +42,33 @@ def test_static_scratch_compaction_matches_regular_entry_point(cuda):
         assert valid == int(kept.sum()) and torch.equal(out_id[:valid], mask[kept])
 
 
+def test_a_call_after_the_warm_up_allocates_nothing(cuda):
+    """After one warm-up call on the device, a call changes neither the free
+    device memory the driver reports nor what torch's allocator holds: the
+    caller's buffers and the built-in array are all it touches."""
+    l = capi.lib()
+    mask, col = make_case(300_001, 0.5, 4, cuda)
+    out_id, out_edge = torch.empty_like(mask), torch.empty_like(col)
+    counter = torch.empty(2, dtype=torch.int32, device=cuda)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call():
+        rc = l.eppgcn_compact_mask_static(mask.data_ptr(), col.data_ptr(), out_id.data_ptr(), out_edge.data_ptr(),
+                                          mask.numel(), counter.data_ptr(), counter.data_ptr() + 4, stream)
+        assert rc == capi.EPP_OK
+        torch.cuda.synchronize()
+
+    call()                                                   # warm-up: module load, address look-up
+    free_before, _ = torch.cuda.mem_get_info(cuda)
+    held_before, reserved_before = torch.cuda.memory_allocated(cuda), torch.cuda.memory_reserved(cuda)
+    for _ in range(2):
+        call()
+    free_after, _ = torch.cuda.mem_get_info(cuda)
+    assert free_after == free_before, "free device memory changed across a call"
+    assert torch.cuda.memory_allocated(cuda) == held_before and torch.cuda.memory_reserved(cuda) == reserved_before
+    assert int(counter[1].item()) == capi.EPP_OK and int(counter[0].item()) == int((mask != -1).sum().item())
+
+
 def test_static_scratch_edge_cases(cuda):
     counter = torch.empty(2, dtype=torch.int32, device=cuda)
     empty = torch.zeros(0, dtype=torch.int32, device=cuda)

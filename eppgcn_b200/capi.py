@@ -25,6 +25,13 @@ SIGNATURES = {
     "eppgcn_last_error": (C.c_char_p, []),
     "eppgcn_spmm_forward": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_spmm_backward_compacted": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
+    "eppgcn_tile_plan_bytes": (_SZ, [_LL, _I, _I]),
+    "eppgcn_tile_plan_from_csr": (_I, [_P, _P, _SZ, _P, _P, _I, _LL, _I, _I, _P]),
+    "eppgcn_tile_plan_from_ids": (_I, [_P, _P, _SZ, _P, _P, _LL, _I, _I, _I, _P]),
+    "eppgcn_pack_scaled_rows": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _I, _P]),
+    "eppgcn_tile_plan_destroy": (None, [_P]),
+    "eppgcn_tile_plan_info": (_I, [_P, _P]),
+    "eppgcn_spmm_tiles": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
     "eppgcn_segment_plan_bytes": (_SZ, [_LL, _I]),
@@ -230,6 +237,83 @@ def spmm_segments(src, col_idx, plan, row_scale=None, out=None):
     check(lib().eppgcn_spmm_segments(
         _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), ld,
         _dev(col_idx, torch.int32, "col_idx"), plan._handle,
+        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, _stream()))
+    return out
+
+
+class TilePlan:
+    """Plan of the tiled aggregation (``eppgcn_tile_plan_*``): the rows of an edge
+    list sorted into length classes, with the plan's own padded copy of the
+    source ids.  Owns the device buffer and the host handle."""
+
+    INFO = ("edges", "rows", "slots", "tiles", "nonempty_rows", "cleared_rows", "atomic_rows",
+            "clears_whole_result")
+
+    def __init__(self, handle, buf, dim):
+        self._handle, self._buf, self.dim = handle, buf, dim
+        out = (_LL * 8)()
+        check(lib().eppgcn_tile_plan_info(handle, out))
+        self.info = dict(zip(self.INFO, [int(v) for v in out]))
+
+    @staticmethod
+    def _buffer(device, num_edges, num_rows, num_sources):
+        nbytes = lib().eppgcn_tile_plan_bytes(int(num_edges), int(num_rows), int(num_sources))
+        return torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=device), nbytes
+
+    @classmethod
+    def from_csr(cls, row_ptr, col_idx, dim, num_sources=None):
+        """Forward plan: row ``r`` owns edges ``[row_ptr[r], row_ptr[r+1])`` of ``col_idx``;
+        ``num_sources`` rows in the source matrix (default: a square graph)."""
+        num_rows, num_edges = row_ptr.numel() - 1, col_idx.numel()
+        num_sources = num_rows if num_sources is None else num_sources
+        buf, nbytes = cls._buffer(row_ptr.device, num_edges, num_rows, num_sources)
+        handle = _P()
+        check(lib().eppgcn_tile_plan_from_csr(C.byref(handle), buf.data_ptr(), nbytes,
+                                              _dev(row_ptr, torch.int32, "row_ptr"),
+                                              _dev(col_idx, torch.int32, "col_idx"), num_rows, num_edges,
+                                              int(num_sources), int(dim), _stream()))
+        return cls(handle, buf, dim)
+
+    @classmethod
+    def from_ids(cls, ids, col_idx, num_edges, num_rows, dim, num_sources=None):
+        """Backward plan: ``ids[e]`` is the row and ``col_idx[e]`` the source of compacted edge ``e < num_edges``."""
+        num_sources = num_rows if num_sources is None else num_sources
+        buf, nbytes = cls._buffer(ids.device, num_edges, num_rows, num_sources)
+        handle = _P()
+        check(lib().eppgcn_tile_plan_from_ids(C.byref(handle), buf.data_ptr(), nbytes, _dev(ids, torch.int32, "ids"),
+                                              _dev(col_idx, torch.int32, "col_idx"), int(num_edges), int(num_rows),
+                                              int(num_sources), int(dim), _stream()))
+        return cls(handle, buf, dim)
+
+    def __del__(self):
+        if getattr(self, "_handle", None) and _lib is not None:
+            _lib.eppgcn_tile_plan_destroy(self._handle)
+            self._handle = None
+
+
+def pack_scaled_rows(x, scale, plan=None, out=None, pad_to=8):
+    """``scale[:, None] * x`` into a buffer whose row stride is the width rounded up to
+    ``pad_to`` floats; with ``plan`` only the rows its edges name are written."""
+    n, dim = x.shape
+    if out is None:
+        ld = (dim + pad_to - 1) // pad_to * pad_to
+        out = torch.empty(n, ld, device=x.device, dtype=torch.float32)[:, :dim]
+    check(lib().eppgcn_pack_scaled_rows(out.data_ptr(), _row_stride(out, "out"), x.data_ptr(), _row_stride(x, "x"),
+                                        None if scale is None else _dev(scale, torch.float32, "scale"),
+                                        None if plan is None else plan._handle, n, dim, _stream()))
+    return out
+
+
+def spmm_tiles(src, plan, row_scale=None, out=None):
+    """``out[r] = row_scale[r] * sum_e src[col_idx[e]]`` over the rows of ``plan``;
+    ``src`` rows already carry their source-side factor and may be padded."""
+    n = plan.info["rows"]
+    dim = src.size(1)
+    ld = _row_stride(src, "src")
+    if out is None:
+        out = torch.empty(n, dim, device=src.device, dtype=torch.float32)
+    check(lib().eppgcn_spmm_tiles(
+        _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), ld, plan._handle,
         None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, _stream()))
     return out
 

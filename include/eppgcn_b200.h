@@ -153,6 +153,54 @@ int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long lo
                          int dim, void *stream);
 
 /* ------------------------------------------------------------------------
+ * Tiled planned aggregation (see eppgcn_spmm_segments for what is computed and
+ * which reference code it stands in for): the plan re-orders the rows by their
+ * number of edges and keeps its own padded copy of the edge list, so that the
+ * lanes of a warp always work on rows of one length class.
+ *
+ *   out[r][:] = row_scale[r] * sum over edges e of row r:  src[col_idx[e]][:]
+ *
+ * eppgcn_tile_plan_from_csr / _from_ids take the edge list (col_idx, device)
+ * besides the row structure: row_ptr [num_rows+1] (device), or the row id of
+ * every edge, `ids` (device, valid prefix of num_edges entries; the edges of a
+ * row must be consecutive, rows may come in any order).  Building copies the
+ * row structure to the host, sorts the rows into classes there (linear time),
+ * fills the padded edge copy on the device and synchronises `stream`.  The
+ * device buffer (eppgcn_tile_plan_bytes, 256-byte aligned) must outlive the
+ * plan; col_idx, row_ptr and ids are not needed after the build.
+ * `dim` selects the row-width class (<= 16 columns, <= 32, <= 64, wider) as for
+ * the segment plan.  eppgcn_tile_plan_info: out8 = {edges, rows, padded edge
+ * slots, tiles, non-empty rows, rows cleared per call, rows summed with atomics
+ * (more than 64 edges), whole result cleared per call}.
+ * num_sources is the number of rows of the source matrix (col_idx values are
+ * below it; num_rows for a square graph); the plan remembers which of them an
+ * edge names.
+ * eppgcn_spmm_tiles: arguments as eppgcn_spmm_segments, minus col_idx.
+ *
+ * eppgcn_pack_scaled_rows prepares the source of a backward aggregation, in
+ * place of the per-edge degrees[...] factor of ours_backward_cuda_kernel
+ * (EPPGCN_kernel.cu:660-663):  dst[r][0..dim) = scale[r] * x[r][0..dim)  into
+ * rows of dst_ld floats (a multiple of 4, 16-byte aligned), only for the rows
+ * the plan's edges name when `plan` is given (the other rows of dst are left
+ * as they are and are never read by eppgcn_spmm_tiles with that plan).
+ */
+typedef struct eppgcn_tile_plan eppgcn_tile_plan;
+size_t eppgcn_tile_plan_bytes(long long num_edges, int num_rows, int num_sources);
+int eppgcn_tile_plan_from_csr(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
+                              const int *row_ptr, const int *col_idx, int num_rows, long long num_edges,
+                              int num_sources, int dim, void *stream);
+int eppgcn_tile_plan_from_ids(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
+                              const int *ids, const int *col_idx, long long num_edges, int num_rows,
+                              int num_sources, int dim, void *stream);
+void eppgcn_tile_plan_destroy(eppgcn_tile_plan *plan);
+int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *out8);
+int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src, long long src_ld,
+                      const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream);
+int eppgcn_pack_scaled_rows(float *dst, long long dst_ld, const float *x, long long ldx,
+                            const float *scale, const eppgcn_tile_plan *plan, int num_rows, int dim,
+                            void *stream);
+
+/* ------------------------------------------------------------------------
  * Dense update of a layer with the source-side factor folded in.
  * Replaces the torch::mm(input, weight) of the forward wrapper
  * (EPPGCN/GCNConv/EPPGCN_kernel.cu:142) for narrow outputs.

@@ -22,7 +22,7 @@ def both():
     return eppgcn_b200.load_gnnadvisor(), ref
 
 
-@pytest.mark.parametrize("workload,back", [("cora", 4), ("pubmed", 32), ("rmat16", 32)])
+@pytest.mark.parametrize("workload,back", [("cora", 4), ("pubmed", 32), ("rmat16", 32), ("rmat19", 32)])
 def test_preparation_and_operators_match_the_reference(both, cuda, workload, back):
     ours, ref = both
     ds = graphs.load_workload(workload, 0)
@@ -30,9 +30,10 @@ def test_preparation_and_operators_match_the_reference(both, cuda, workload, bac
     part = int(ds.avg_degree)
     ip = ds.row_pointers
     assert ds.graph.indptr[-1] > ds.graph.indptr[-2] and e < 2 ** 24     # inside the reference's build_part range
-    pr, nr = ref.build_part(part, ip)
     po, no = ours.build_part(part, ip)
-    assert torch.equal(pr.int(), po) and torch.equal(nr.int(), no)
+    if e < 2_000_000:        # the reference fills its outputs element by element: minutes beyond this size
+        pr, nr = ref.build_part(part, ip)
+        assert torch.equal(pr.int(), po) and torch.equal(nr.int(), no)
     pp, p2n = po.to(cuda), no.to(cuda)
     row, col, deg = ip.to(cuda), ds.column_index.to(cuda), ds.degrees.to(cuda)
     train = ds.train_mask.to(cuda)

@@ -1,0 +1,170 @@
+"""The tiled planned aggregation (rows sorted into length classes) through the
+C-ABI against the float64 oracle and against the group kernel.
+Tolerance: |got - want| <= 2e-6 + 2e-5*|want| (the source rows are pre-scaled in
+fp32 before the sum)."""
+import numpy as np
+import pytest
+import torch
+
+from eppgcn_b200 import capi
+from oracle import epp_oracle as O
+from tests.helpers import assert_close, degrees_of, random_csr, t
+from tests.test_gpu_segments import GRAPHS, make_path, padded_rows
+
+pytestmark = pytest.mark.gpu
+
+GRAPHS = dict(GRAPHS, wide=dict(n=300, avg_deg=30.0, seed=8, hubs=4, hub_deg=290),
+              single=dict(n=64, avg_deg=1.0, seed=9))
+
+
+def forward_case(cuda, indptr, indices, dim, pad_to=4, seed=0, out=None):
+    n = len(indptr) - 1
+    rng = np.random.Generator(np.random.PCG64(seed))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    deg = degrees_of(indptr)
+    col = t(indices, cuda) if len(indices) else torch.zeros(0, dtype=torch.int32, device=cuda)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), col, dim)
+    src = padded_rows(feat * deg[:, None], cuda, pad_to)
+    got = capi.spmm_tiles(src, plan, t(deg, cuda), out=out)
+    torch.cuda.synchronize()
+    return got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), plan
+
+
+@pytest.mark.parametrize("graph", sorted(GRAPHS))
+@pytest.mark.parametrize("dim", [1, 3, 4, 5, 16, 22, 32, 33, 64, 96, 128, 130, 200])
+def test_forward_dims(cuda, graph, dim):
+    indptr, indices = random_csr(**GRAPHS[graph])
+    got, want, _ = forward_case(cuda, indptr, indices, dim)
+    assert np.isfinite(got).all()
+    assert_close(got, want, 2e-5, 2e-6, what=f"tiled forward {graph} dim {dim}")
+
+
+def test_plan_counts(cuda):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda), 16)
+    info, deg = plan.info, np.diff(indptr)
+    assert info["edges"] == len(indices) and info["rows"] == n
+    assert info["nonempty_rows"] == int((deg > 0).sum()) and info["atomic_rows"] == int((deg > 64).sum())
+    assert info["cleared_rows"] == int((deg == 0).sum() + (deg > 64).sum())
+    width = np.where(deg >= 5, (deg + 7) // 8 * 8, np.where(deg >= 3, 4, deg))
+    pieces = np.where(deg > 64, (deg // 64) * 64 + np.where(deg % 64 >= 5, (deg % 64 + 7) // 8 * 8,
+                                                             np.where(deg % 64 >= 3, 4, deg % 64)), width)
+    assert info["slots"] >= int(pieces.sum()) and info["slots"] % 8 == 0
+
+
+def test_empty_graph_and_overwrite(cuda):
+    n, dim = 50, 16
+    indptr = np.zeros(n + 1, dtype=np.int32)
+    out = torch.full((n, dim), 7.0, device=cuda)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), torch.zeros(0, dtype=torch.int32, device=cuda), dim)
+    capi.spmm_tiles(torch.ones(n, dim, device=cuda), plan, torch.ones(n, device=cuda), out=out)
+    assert torch.count_nonzero(out).item() == 0, "rows without edges must come back zero"
+
+
+def test_plan_of_another_width_class_is_refused(cuda):
+    indptr, indices = random_csr(**GRAPHS["dense"])
+    n = len(indptr) - 1
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda), 16)
+    with pytest.raises(capi.EppError):
+        capi.spmm_tiles(torch.zeros(n, 64, device=cuda), plan)
+
+
+def test_rows_that_are_not_consecutive_are_refused(cuda):
+    ids = torch.tensor([0, 0, 1, 0], dtype=torch.int32, device=cuda)
+    with pytest.raises(capi.EppError) as e:
+        capi.TilePlan.from_ids(ids, ids.clone(), 4, 2, 16)
+    assert e.value.status == capi.EPP_ERR_BAD_ARG
+
+
+def test_result_overwrites_and_is_repeatable(cuda):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    out = torch.full((n, 16), 7.0, device=cuda)
+    a, want, _ = forward_case(cuda, indptr, indices, 16, out=out)
+    assert_close(a, want, 2e-5, 2e-6, what="first call into a dirty buffer")
+    b, _, _ = forward_case(cuda, indptr, indices, 16, out=out)
+    assert_close(b, want, 2e-5, 2e-6, what="second call into the previous result")
+
+
+@pytest.mark.parametrize("dim,left,right", [(8, 8, 0), (8, 4, 4), (22, 2, 0), (5, 3, 1), (7, 1, 0), (64, 64, 64)])
+def test_result_lands_in_a_column_block(cuda, dim, left, right):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    wide = torch.full((n, left + dim + right), 7.0, device=cuda)
+    got, want, _ = forward_case(cuda, indptr, indices, dim, out=wide[:, left:left + dim])
+    assert_close(got, want, 2e-5, 2e-6, what="tiled forward column block")
+    full = wide.cpu().numpy()
+    assert (full[:, :left] == 7.0).all() and (full[:, left + dim:] == 7.0).all()
+
+
+@pytest.mark.parametrize("dim", [1, 4, 16, 22, 64, 128, 150])
+@pytest.mark.parametrize("ratio", [0.0, 0.02, 0.15, 1.0])
+def test_backward_over_the_compacted_path(cuda, dim, ratio):
+    """Plan from the compacted row ids; rows off the path come back zero."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    d_out = rng.standard_normal((n, dim)).astype(np.float32)
+    src = padded_rows(d_out * deg[:, None], cuda, 8)
+    for conv in make_path(indptr, indices, ratio, 2, 6, 8, seed=dim + 1):
+        plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n, dim)
+        out = torch.full((n, dim), 5.0, device=cuda)
+        capi.spmm_tiles(src, plan, t(deg, cuda), out=out)
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, d_out,
+                                         conv["numParts"])
+        got = out.cpu().numpy()
+        assert_close(got, want, 2e-5, 2e-6, what=f"tiled backward dim {dim} ratio {ratio}")
+        assert np.all(got[conv["node_degs"] == 0] == 0), "rows off the path must come back zero"
+        assert plan.info["nonempty_rows"] == int((conv["node_degs"] > 0).sum())
+
+
+@pytest.mark.parametrize("dim", [16, 22, 64])
+def test_agrees_with_the_group_kernel_on_rmat(cuda, dim):
+    """Both kernels on a power-law graph with hub rows of tens of thousands of edges."""
+    from eppgcn_b200 import graphs
+    g = graphs.make_graph("rmat16", 0)
+    n, e = g.num_nodes, g.num_edges
+    deg = degrees_of(g.indptr)
+    pp, p2n = O.build_part(max(e // n, 1), g.indptr)
+    gen = torch.Generator(device=cuda).manual_seed(dim)
+    ld = (dim + 7) // 8 * 8
+    src = torch.randn(n, ld, device=cuda, generator=gen)[:, :dim]
+    row, col, d = t(g.indptr, cuda), t(g.indices, cuda), t(deg, cuda)
+    a = capi.spmm_forward(src, row, col, d, t(pp, cuda), t(p2n, cuda), e // n, prescaled=True)
+    b = capi.spmm_tiles(src, capi.TilePlan.from_csr(row, col, dim), d)
+    scale = a.abs().max().item()
+    assert torch.allclose(a, b, rtol=2e-5, atol=2e-6 * scale)
+
+
+@pytest.mark.parametrize("dim", [1, 5, 7, 16, 22, 64])
+@pytest.mark.parametrize("view", ["dense", "column_block"])
+def test_pack_scaled_rows_writes_the_rows_the_path_names(cuda, dim, view):
+    """The backward's source: deg[r] * d_out[r] for the rows the compacted edges name, into padded rows;
+    every other row of the buffer is left alone."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    conv = make_path(indptr, indices, 0.1, 2, 6, 8, seed=dim)[1]
+    plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n, dim)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    x = rng.standard_normal((n, dim + 3)).astype(np.float32)
+    xd = t(x, cuda)
+    xv = xd[:, 1:1 + dim] if view == "column_block" else xd[:, :dim].contiguous()     # 4-byte or row aligned source
+    ld = (dim + 7) // 8 * 8
+    dst = torch.full((n, ld), 7.0, device=cuda)
+    capi.pack_scaled_rows(xv, t(deg, cuda), plan, out=dst[:, :dim])
+    used = np.zeros(n, dtype=bool)
+    used[conv["edgeList"][:conv["valid_len"]]] = True
+    got = dst.cpu().numpy()
+    want = xv.cpu().numpy() * deg[:, None]
+    np.testing.assert_array_equal(got[used][:, :dim], want[used])
+    assert (got[~used] == 7.0).all(), "rows no edge names must not be written"
+    # and the aggregation over the packed rows equals the oracle's
+    out = capi.spmm_tiles(dst[:, :dim], plan, t(deg, cuda))
+    want_agg = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg,
+                                         xv.cpu().numpy(), conv["numParts"])
+    assert_close(out.cpu().numpy(), want_agg, 2e-5, 2e-6, what=f"backward over packed rows dim {dim}")
+    all_rows = capi.pack_scaled_rows(xv, t(deg, cuda))
+    np.testing.assert_array_equal(all_rows.cpu().numpy(), want)

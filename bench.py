@@ -2,27 +2,36 @@
 """Benchmark of the GCN aggregation hot path.
 
 Metric: ms per epoch of the forward + backward neighbour aggregation of a
-2-layer GCN (hidden 16, 22 classes) -- two forward SpMMs over the whole graph
-and two backward SpMMs over the prepared execution path -- on a seeded R-MAT
-scale-21 graph (2,097,152 vertices, 35,651,584 directed edges with self loops).
+2-layer GCN (hidden 16, 22 classes) -- two forward aggregations over the whole
+graph and two backward aggregations over the prepared execution path -- on a
+seeded R-MAT scale-21 graph (2,097,152 vertices, 35,651,584 directed edges with
+self loops) unless another workload is named.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--workload NAME] [--train-ratio R] [--kernel tiles|groups]
 
 * ``value``  device-resident: inputs already in HBM, K steps timed with CUDA
-  events around the C-ABI launches.
+  events around the C-ABI launches the operator module makes per epoch (the
+  planned tile kernel; for a backward layer also the packing of its source
+  rows and the clearing of the result).
 * ``e2e``    the same four aggregations through the C-ABI with HOST buffers:
   every step copies its four input matrices from pinned host memory and
   copies the four results back.
 * ``roofline``  the dominant kernel's compulsory bytes / its CUDA-event time,
   against the measured HBM copy bandwidth.
+* ``check``  outside the timed region: every aggregation's result on sampled
+  rows (the highest-degree rows among them) against the float64 oracle.
+* ``ref_cuda``  the reference's own CUDA operators (unmodified build under
+  oracle/_ref, when present) on the same workload, run in a child process.
 * ``cpu_baseline`` / ``--impl reference``  the CPU GCN path (torch.sparse CSR
   SpMM, fp32, all host cores) on the same graph: the same four aggregations,
   over the whole graph in both directions (the CPU path has no execution-path
-  preparation).
+  preparation, so its backward is the uncompacted one).
 """
 from __future__ import annotations
 
 import argparse
+import hashlib
 import json
 import os
 import statistics
@@ -37,10 +46,7 @@ import torch
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of each aggregation kernel on the default
-# workload (rmat21, seed 0), from the ncu capture summarised in profiles/staged_spmm_rmat21_ncu_full.md.
-NCU_DRAM_TRAFFIC = {"fwd_d16": 590_400_000, "fwd_d22": 903_200_000,
-                    "bwd_conv2_d22": 136_700_000, "bwd_conv1_d16": 492_700_000}
+METRIC = "2-layer GCN ms/epoch (fwd+bwd aggregation)"
 
 
 def log(*a):
@@ -54,6 +60,28 @@ def measured_peak_gbs():
             return float(json.load(f)["hbm_gbs"]), "measured"
     except Exception:
         return 6650.0, "fallback"
+
+
+def recorded_traffic(kernel_source: str):
+    """DRAM bytes per launch from the committed profiler record, valid only while the kernel source it
+    was captured at is unchanged: the record, or {}."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_dram_traffic.json")) as f:
+            rec = json.load(f)
+        with open(os.path.join(ROOT, "eppgcn_b200", "csrc", kernel_source), "rb") as f:
+            digest = hashlib.sha1(f.read()).hexdigest()[:16]
+        if rec.get("source") == kernel_source and rec.get("source_sha1_16") == digest:
+            return rec
+    except Exception:
+        pass
+    return {}
+
+
+def workload_string(name, spec, n, e, dims, ratio, part_size, backsize):
+    """One wording of the workload for both arms, so that their lines can be matched."""
+    kind = "R-MAT a=.57 b=.19 c=.19" if spec["kind"] == "rmat" else f"Chung-Lu exponent {spec['exponent']}"
+    return (f"{name}: {kind}, N={n}, E={e} directed incl. self loops, dims {'/'.join(str(d) for d in dims)}, "
+            f"train_ratio {ratio}, group size {part_size}, backward part size {backsize}")
 
 
 class ClockSampler:
@@ -138,10 +166,14 @@ def run_cpu(graph, dims, steps, warmup, budget_s=25.0):
     a = cpu_gcn.normalised_csr(graph)
     g = torch.Generator().manual_seed(0)
     mats = [torch.randn(graph.num_nodes, d, generator=g) for d in (dims[0], dims[1], dims[1], dims[0])]
-    for _ in range(max(1, min(warmup, 2))):
+    one, spent = 1.0, 0.0
+    for _ in range(max(1, warmup)):
         t0 = time.perf_counter()
         cpu_gcn.aggregation_epoch(a, mats)
         one = time.perf_counter() - t0
+        spent += one
+        if spent > budget_s / 3:             # a slow host: the warm-up is cut short
+            break
     epochs = max(1, min(steps, int(budget_s / max(one, 1e-6))))
     t0 = time.perf_counter()
     for _ in range(epochs):
@@ -150,16 +182,36 @@ def run_cpu(graph, dims, steps, warmup, budget_s=25.0):
     return ms, cores, epochs
 
 
+def run_cpu_training(ds, spec, epochs):
+    """Whole training epochs of the dense-update / sparse-aggregate GCN on the CPU (forward, loss on
+    the train rows, backward, Adam), for the CPU-only configuration: ms/epoch."""
+    from oracle import cpu_gcn
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    a = cpu_gcn.normalised_csr(ds.graph)
+    g = torch.Generator().manual_seed(1)
+    dims = [spec["dim"], spec["hidden"], spec["classes"]]
+    weights = [torch.nn.Parameter((torch.rand(dims[i], dims[i + 1], generator=g) * 2 - 1) / dims[i + 1] ** 0.5)
+               for i in range(2)]
+    opt = torch.optim.Adam(weights, lr=0.01)
+    x, y, mask = ds.x.cpu(), ds.y.cpu(), ds.train_mask.cpu()
+    for _ in range(3):
+        cpu_gcn.gcn_epoch(a, x, weights, y, mask, opt)
+    t0 = time.perf_counter()
+    for _ in range(epochs):
+        cpu_gcn.gcn_epoch(a, x, weights, y, mask, opt)
+    return (time.perf_counter() - t0) * 1e3 / epochs
+
+
 # ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
 class HotPath:
-    """Device-resident state of one rank: CSR slice, groups, prepared path."""
+    """Device-resident state of one GPU: CSR, groups, prepared path, aggregation plans."""
 
-    def __init__(self, ds, dev, back_size=32):
+    def __init__(self, ds, dev, back_size=32, kernel="tiles"):
         import eppgcn_b200
         from eppgcn_b200 import capi
-        self.capi, self.dev = capi, dev
+        self.capi, self.dev, self.kernel = capi, dev, kernel
         gnna = eppgcn_b200.load_gnnadvisor()
         n, e, L = ds.num_nodes, ds.num_edges, ds.num_layers
         self.n, self.e = n, e
@@ -188,17 +240,48 @@ class HotPath:
         torch.cuda.synchronize(dev)
         self.prep_s = time.perf_counter() - t0
         self.back_size = back_size
+        # plans of the tiled kernel, one per edge list (what the operator module builds at first use)
+        self.plan_s = None
+        if kernel == "tiles":
+            t0 = time.perf_counter()
+            self.fwd_plan = capi.TilePlan.from_csr(self.row, self.col)
+            for p in self.path:
+                p["plan"] = capi.TilePlan.from_ids(p["id"], p["edges"], p["valid"], n)
+                p["src"] = {}
+            torch.cuda.synchronize(dev)
+            self.plan_s = time.perf_counter() - t0
 
     def forward(self, feat, out):
         """Forward aggregation as the operator module runs it: the update step has already folded
         deg[col] into the rows of `feat`."""
+        if self.kernel == "tiles":
+            return self.capi.spmm_tiles(feat, self.fwd_plan, self.deg, out=out)
         return self.capi.spmm_forward(feat, self.row, self.col, self.deg, self.pp, self.p2n, self.part_size, out=out,
                                       prescaled=True)
 
     def backward(self, i, d_out, out):
+        """Backward aggregation of convolution i+1 as the operator module runs it: with the plan, the
+        source rows are packed (scaled by deg, padded rows) and aggregated; else the group kernel."""
         p = self.path[i]
+        if self.kernel == "tiles":
+            d = d_out.size(1)
+            if d not in p["src"]:
+                p["src"][d] = torch.empty(self.n, (d + 7) // 8 * 8, device=self.dev)[:, :d]
+            src = self.capi.pack_scaled_rows(d_out, self.deg, p["plan"], out=p["src"][d])
+            return self.capi.spmm_tiles(src, p["plan"], self.deg, out=out)
         return self.capi.spmm_backward_compacted(d_out, p["id"], p["pp"], p["edges"], self.deg, p["parts"],
                                                  self.back_size, out=out)
+
+    def launches_per_step(self):
+        """This library's kernels in one epoch of four aggregations."""
+        if self.kernel != "tiles":
+            return 4
+        k = 0
+        for plan in (self.fwd_plan, self.fwd_plan):
+            k += 1 + (1 if plan.info["cleared_rows"] and not plan.info["clears_whole_result"] else 0)
+        for p in self.path:
+            k += 2 + (1 if p["plan"].info["cleared_rows"] and not p["plan"].info["clears_whole_result"] else 0)
+        return k
 
 
 def padded(n, d, dev, gen):
@@ -216,6 +299,138 @@ def bytes_backward(n, d, p, src_rows):
     return 4 * p["valid"] + 4 * (p["parts"] + 1) + 4 * p["parts"] + 4 * d * src_rows + 4 * (p["rows"] + src_rows) + 4 * d * n
 
 
+def sample_rows(indptr, count, seed):
+    """Rows to check: the 1,000 rows with the most edges, then a seeded uniform sample."""
+    n = len(indptr) - 1
+    deg = np.diff(indptr)
+    top = np.argsort(-deg, kind="stable")[:min(1000, n)]
+    rng = np.random.Generator(np.random.PCG64(seed))
+    rest = rng.choice(n, size=min(count, n), replace=False)
+    return np.unique(np.concatenate([top, rest]))
+
+
+def check_against_oracle(ds, hp, ins, outs, dims, rows_wanted=200_000):
+    """Each of the four results on sampled rows against the float64 oracle.  The forward inputs are
+    pre-scaled rows, so the oracle gets rows divided back by deg in float64; tolerance
+    |got - want| <= 2e-6 + 2e-5 |want|.  Returns the `check` object of the bench line."""
+    from oracle import epp_oracle as O
+    ip, ix = ds.graph.indptr, ds.graph.indices
+    deg = hp.deg.cpu().numpy().astype(np.float64)
+    rows = sample_rows(ip, rows_wanted, 7)
+    worst, detail = -np.inf, {}
+    for k in range(4):
+        x = ins[k].cpu().numpy().astype(np.float64)
+        got = outs[k].cpu().numpy()[rows]
+        if k < 2:
+            want = O.spmm_rows(ip, ix, rows, x, row_scale=deg)                 # rows already carry deg[col]
+        else:
+            p = hp.path[1 if k == 2 else 0]
+            v = p["valid"]
+            want = O.spmm_rows_from_pairs(p["id"][:v].cpu().numpy(), p["edges"][:v].cpu().numpy(), hp.n, rows,
+                                          x * deg[:, None], row_scale=deg)
+        excess = float((np.abs(got - want) - (2e-6 + 2e-5 * np.abs(want))).max())
+        worst = max(worst, excess)
+        detail[("fwd_l1", "fwd_l2", "bwd_conv2", "bwd_conv1")[k]] = excess
+    return {"rows": int(rows.size), "max_excess": worst, "ok": bool(worst <= 0),
+            "tolerance": "|got-want| <= 2e-6 + 2e-5|want| against float64, sampled rows incl. the 1000 of highest degree",
+            "per_aggregation": detail}
+
+
+def ref_cuda_child(args):
+    """Child process: the reference's own CUDA operators on the workload, timed by the reference's own
+    event timers (for_agg_time / back_agg_time, EPPGCN_kernel.cu:96-116); prints one JSON object."""
+    from eppgcn_b200 import graphs
+    from oracle.ref_loader import load_reference
+    ref = load_reference()
+    if ref is None:
+        print(json.dumps({"unavailable": "oracle/_ref holds no build of the reference's extension"}), flush=True)
+        return
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    spec = graphs.WORKLOADS[args.workload]
+    ds = graphs.load_workload(args.workload, args.seed, train_ratio=args.train_ratio)
+    hp = HotPath(ds, dev, args.backsize, kernel="groups")          # int32 metadata from this library's preparation
+    n = hp.n
+    dims = [spec["dim"], spec["hidden"], spec["classes"]]
+    gen = torch.Generator(device=dev).manual_seed(args.seed)
+    xs = [torch.randn(n, dims[i], device=dev, generator=gen) for i in range(2)]
+    ws = [(torch.rand(dims[i], dims[i + 1], device=dev, generator=gen) - 0.5) / 2 for i in range(2)]
+    douts = [torch.randn(n, dims[i + 1], device=dev, generator=gen) for i in range(2)]
+    dim_worker = [min(dims[0], 32), min(dims[1], 32)]
+
+    def epoch():
+        for i in range(2):
+            ref.forward(xs[i], ws[i], hp.row, hp.col, hp.deg, hp.pp, hp.p2n, hp.part_size, dim_worker[i], 8)
+        for i in (1, 0):
+            p = hp.path[i]
+            ref.ours_backward(douts[i], xs[i], ws[i], p["id"], p["pp"], p["edges"], hp.deg, hp.back_size, p["parts"],
+                              i + 1, 4, 16)
+
+    for _ in range(2):
+        epoch()
+    torch.cuda.synchronize()
+    ref.clear_time()
+    epochs = max(3, min(args.steps, 10))
+    for _ in range(epochs):
+        epoch()
+    torch.cuda.synchronize()
+    # the reference prints its timers with printf: catch file descriptor 1
+    sys.stdout.flush()
+    r, w = os.pipe()
+    saved = os.dup(1)
+    os.dup2(w, 1)
+    try:
+        ref.print_time()
+        import ctypes
+        ctypes.CDLL(None).fflush(None)
+    finally:
+        os.dup2(saved, 1)
+        os.close(w)
+    text = os.read(r, 1 << 16).decode()
+    os.close(r)
+    vals = {}
+    for line in text.splitlines():
+        if ":" in line:
+            key, _, v = line.partition(":")
+            try:
+                vals[key.strip()] = float(v)
+            except ValueError:
+                pass
+    fwd, bwd = vals.get("for_agg_time"), vals.get("back_agg_time")
+    if fwd is None or bwd is None:
+        print(json.dumps({"unavailable": f"could not read the reference's timers: {text!r}"}), flush=True)
+        return
+    print(json.dumps({"ms_per_epoch": round((fwd + bwd) * 1e3 / epochs, 4),
+                      "forward_ms": round(fwd * 1e3 / epochs, 4), "backward_ms": round(bwd * 1e3 / epochs, 4),
+                      "per_layer_backward_ms": {k: round(v * 1e3 / epochs, 4) for k, v in vals.items()
+                                                if k.startswith("l") and k.endswith("_back_agg_time")},
+                      "epochs": epochs, "workload": args.workload,
+                      "what": "the reference's spmm_forward_cuda_kernel and ours_backward_cuda_kernel (unmodified "
+                              "sources compiled for sm_100), its own event timers, same graph, seed, masks and "
+                              "int32 partition metadata"}), flush=True)
+
+
+def run_ref_cuda(args, timeout_s=240):
+    """Runs the reference-kernel leg in a child process, so that nothing it does can take the bench down."""
+    if not os.path.isdir(os.path.join(ROOT, "oracle", "_ref")):
+        return {"unavailable": "oracle/_ref holds no build of the reference's extension"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--ref-cuda-child", "--workload", args.workload, "--seed",
+           str(args.seed), "--backsize", str(args.backsize), "--steps", str(args.steps)]
+    if args.train_ratio is not None:
+        cmd += ["--train-ratio", str(args.train_ratio)]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": f"the reference-kernel leg did not finish within {timeout_s} s"}
+    for line in reversed(r.stdout.splitlines()):
+        if line.startswith("{"):
+            try:
+                return json.loads(line)
+            except ValueError:
+                break
+    return {"unavailable": f"the reference-kernel leg exited with code {r.returncode}: {r.stderr[-300:]!r}"}
+
+
 def run_gpu(args):
     from eppgcn_b200 import graphs
     rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
@@ -224,21 +439,20 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU fallback")
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
-    spec0 = graphs.WORKLOADS[args.workload]
-    if world > 1 or spec0.get("draw") == "device":
+    spec = graphs.WORKLOADS[args.workload]
+    if world > 1 or spec.get("draw") == "device":
         # several ranks, or a workload that is drawn on the GPU: the row-partitioned driver (also at one rank)
         import bench_multi
         return bench_multi.run_bench(args, rank, world, dev)
 
-    spec = graphs.WORKLOADS[args.workload]
+    ratio = spec["train_ratio"] if args.train_ratio is None else args.train_ratio
     t0 = time.perf_counter()
-    ds = graphs.load_workload(args.workload, args.seed)
+    ds = graphs.load_workload(args.workload, args.seed, train_ratio=args.train_ratio)
     log(f"[bench] workload {args.workload}: N={ds.num_nodes} E={ds.num_edges} ({time.perf_counter() - t0:.1f}s)")
     graph = ds.graph
     n, e = ds.num_nodes, ds.num_edges
     dims = [spec["hidden"], spec["classes"]]
-    src_rows = [int(ds.train_mask.sum())]           # rows of d_out the last convolution's backward reads
-    hp = HotPath(ds, dev, args.backsize)
+    hp = HotPath(ds, dev, args.backsize, args.kernel)
     src_rows = [int(ds.ngh_masks[0].sum().item()), int(ds.train_mask.sum().item())]   # conv1, conv2
     gen = torch.Generator(device=dev).manual_seed(args.seed)
     ins = [padded(n, dims[0], dev, gen), padded(n, dims[1], dev, gen),
@@ -247,10 +461,12 @@ def run_gpu(args):
     names = [f"fwd_d{dims[0]}", f"fwd_d{dims[1]}", f"bwd_conv2_d{dims[1]}", f"bwd_conv1_d{dims[0]}"]
     algo = [bytes_forward(n, e, dims[0]), bytes_forward(n, e, dims[1]),
             bytes_backward(n, dims[1], hp.path[1], src_rows[1]), bytes_backward(n, dims[0], hp.path[0], src_rows[0])]
+    fns = [lambda: hp.forward(ins[0], outs[0]), lambda: hp.forward(ins[1], outs[1]),
+           lambda: hp.backward(1, ins[2], outs[2]), lambda: hp.backward(0, ins[3], outs[3])]
 
     def step():
-        hp.forward(ins[0], outs[0]); hp.forward(ins[1], outs[1])
-        hp.backward(1, ins[2], outs[2]); hp.backward(0, ins[3], outs[3])
+        for fn in fns:
+            fn()
 
     stream = torch.cuda.current_stream()
     # -- whole-step timing (the clock sampler runs from the warm-up to the last per-kernel launch) ----
@@ -266,17 +482,15 @@ def run_gpu(args):
         ev1.record(stream)
         torch.cuda.synchronize()
         ms_step = ev0.elapsed_time(ev1) / args.steps
-        # -- per-kernel timing (same launches, one event pair each) ----------
+        # -- per-aggregation timing (same launches, one event pair each) ----------
         per = [[] for _ in range(4)]
-        fns = [lambda: hp.forward(ins[0], outs[0]), lambda: hp.forward(ins[1], outs[1]),
-               lambda: hp.backward(1, ins[2], outs[2]), lambda: hp.backward(0, ins[3], outs[3])]
         for _ in range(args.steps):
             for k, fn in enumerate(fns):
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream); fn(); b.record(stream)
                 per[k].append((a, b))
         torch.cuda.synchronize()
-        # -- the bare gather of the two forward aggregations: the floor on this GPU -------
+        # -- the bare gather of the two forward aggregations, in CSR order --------
         floor = []
         sink = torch.zeros(1, device=dev)
         for k in range(2):
@@ -302,29 +516,39 @@ def run_gpu(args):
     peak, peak_src = measured_peak_gbs()
     kernels = {nm: {"ms": round(ms, 4), "algorithmic_mb": round(by / 1e6, 1), "gbs": round(by / ms / 1e6, 1),
                     "frac": round(by / ms / 1e6 / peak, 4)} for nm, ms, by in zip(names, kern_ms, algo)}
+    upd_bytes = 4 * n * (spec["dim"] + dims[0])
     kernels[f"update_k{spec['dim']}_d{dims[0]}"] = {
-        "ms": round(update_ms, 4), "algorithmic_mb": round(4 * n * (spec["dim"] + dims[0]) / 1e6, 1),
-        "gbs": round(4 * n * (spec["dim"] + dims[0]) / update_ms / 1e6, 1),
-        "frac": round(4 * n * (spec["dim"] + dims[0]) / update_ms / 1e6 / peak, 4),
+        "ms": round(update_ms, 4), "algorithmic_mb": round(upd_bytes / 1e6, 1),
+        "gbs": round(upd_bytes / update_ms / 1e6, 1), "frac": round(upd_bytes / update_ms / 1e6 / peak, 4),
         "note": "diag(deg) (X W) with FP32 FMA; feeds the forward aggregation, outside the metric"}
     for k in range(2):
         row_bytes = ins[k].stride(0) * 4
-        kernels[names[k]]["gather_floor_ms"] = round(floor[k], 4)
-        kernels[names[k]]["gather_floor_tbs"] = round(e * row_bytes / floor[k] / 1e9, 2)
-        kernels[names[k]]["of_gather_floor"] = round(floor[k] / kern_ms[k], 3)
+        kernels[names[k]]["csr_order_gather_ms"] = round(floor[k], 4)
+        kernels[names[k]]["csr_order_gather_tbs"] = round(e * row_bytes / floor[k] / 1e9, 2)
     top = max(range(4), key=lambda k: kern_ms[k])
+    traffic = recorded_traffic("tiled_spmm.cu") if args.kernel == "tiles" else {}
     roofline = {"bound": "hbm", "kernel": names[top], "achieved": round(algo[top] / kern_ms[top] / 1e6, 1),
                 "peak": peak, "peak_source": peak_src, "unit": "GB/s",
                 "frac": round(algo[top] / kern_ms[top] / 1e6 / peak, 4), "traffic": None,
                 "algorithmic_bytes": algo[top], "ms": round(kern_ms[top], 4)}
-    if args.workload == "rmat21" and args.seed == 0:
-        roofline["traffic"] = NCU_DRAM_TRAFFIC.get(names[top])
-        roofline["traffic_note"] = "dram__bytes_read+write of one launch, ncu capture summarised under profiles/"
+    if traffic.get("workload") == args.workload and traffic.get("seed") == args.seed and ratio == spec["train_ratio"]:
+        roofline["traffic"] = traffic.get("dram_bytes_per_launch", {}).get(names[top])
+        roofline["traffic_note"] = "dram__bytes_read+write of one aggregation from the recorded ncu capture of this source"
 
-    # -- e2e: host buffers through the C-ABI ------------------------------------
     if args.kernels_only:
         print(json.dumps({"value": round(ms_step, 4), "kernels": kernels, "roofline": roofline}), flush=True)
         return
+    # -- parity at the size that was timed (outside the timed region) -----------------
+    check = None
+    if not args.no_check:
+        step()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        check = check_against_oracle(ds, hp, ins, outs, dims)
+        check["seconds"] = round(time.perf_counter() - t0, 1)
+        log(f"[bench] check: {check}")
+
+    # -- e2e: host buffers through the C-ABI ------------------------------------
     host_in = [torch.empty(x.shape, pin_memory=True).copy_(x) for x in ins]
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
     stage = [padded(n, dims[0], dev, gen), padded(n, dims[1], dev, gen),
@@ -371,12 +595,13 @@ def run_gpu(args):
     e2e_ms = ev0.elapsed_time(ev1) / e2e_steps
     h2d = sum(x.numel() * 4 for x in ins)
     d2h = sum(o.numel() * 4 for o in outs)
+    del host_in, host_out, stage
 
     # -- full training epoch through the operator module (context) --------------
     epoch_full = None
     if not args.no_full_epoch:
         from eppgcn_b200.train import GCNTrainer
-        ds2 = graphs.load_workload(args.workload, args.seed)
+        ds2 = graphs.load_workload(args.workload, args.seed, train_ratio=args.train_ratio)
         tr = GCNTrainer(ds2, hidden=spec["hidden"], backsize_mode="constant", backsize=args.backsize)
         for _ in range(3):
             tr.train_epoch()
@@ -390,29 +615,40 @@ def run_gpu(args):
                       "what": "forward + log_softmax/nll_loss + backward + Adam through GCNConv, X resident"}
         del tr, ds2
 
+    # -- the reference's own kernels on this GPU, in a child process -----------------
+    ref_cuda = None
+    if not args.no_ref_cuda:
+        torch.cuda.empty_cache()
+        ref_cuda = run_ref_cuda(args)
+        log(f"[bench] ref_cuda: {ref_cuda}")
+
     # -- CPU baseline on this box's host cores -------------------------------------
     cpu = None
     if not args.no_cpu_baseline:
         ms, cores, epochs = run_cpu(graph, dims, 5, 1, budget_s=20.0)
         cpu = {"value": round(ms, 2), "unit": "ms/epoch", "cores": cores, "kind": "port",
-               "sample": f"{epochs} epoch(s) of the full workload: 4 torch.sparse CSR SpMMs over the whole graph"}
+               "sample": f"{epochs} epoch(s) of the full workload: 4 torch.sparse CSR SpMMs over the whole graph "
+                         f"(the CPU path has no execution-path preparation: its backward is the uncompacted one)"}
 
+    active = [p["valid"] for p in hp.path]
     line = {
-        "metric": "2-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms_step, 4), "unit": "ms/epoch",
+        "metric": METRIC, "value": round(ms_step, 4), "unit": "ms/epoch",
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: R-MAT a=.57 b=.19 c=.19, N={n}, E={e} directed incl. self loops, "
-                               f"dims {dims[0]}/{dims[1]}, train_ratio {spec['train_ratio']}, "
-                               f"group size {hp.part_size}, backward part size {args.backsize}",
+        "config": {"workload": workload_string(args.workload, spec, n, e, dims, ratio, hp.part_size, args.backsize),
                    "seed": args.seed, "l2": "inputs exceed L2: each step streams >1 GB of distinct data",
-                   "parallelism": "single GPU"},
-        "kernels": kernels, "roofline": roofline, "clocks": clocks.summary(),
+                   "parallelism": "single GPU",
+                   "kernel": "tiled plan (rows in width classes, padded edge copy)" if args.kernel == "tiles"
+                             else "neighbour-group kernel"},
+        "kernels": kernels, "roofline": roofline, "clocks": clocks.summary(), "check": check,
         "e2e": {"value": round(e2e_ms, 4), "unit": "ms/epoch", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "what": "same four aggregations through the C-ABI, inputs from pinned host memory, results copied back"},
-        "gpu_launches": 4 * args.steps,
+        "gpu_launches": hp.launches_per_step() * args.steps,
         "prep": {"build_part_s": round(hp.build_part_s, 3), "mask_compact_split_s": round(hp.prep_s, 4),
-                 "active_edges": [p["valid"] for p in hp.path], "parts": [p["parts"] for p in hp.path]},
-        "epoch_full": epoch_full, "cpu_baseline": cpu,
+                 "aggregation_plans_s": None if hp.plan_s is None else round(hp.plan_s, 3),
+                 "active_edges": active, "active_edge_share": [round(v / e, 4) for v in active],
+                 "parts": [p["parts"] for p in hp.path]},
+        "epoch_full": epoch_full, "ref_cuda": ref_cuda, "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)
 
@@ -428,21 +664,37 @@ def run_reference(args):
                           "generation takes too long for a bench run); the CPU arm covers the host-drawn workloads"}),
               flush=True)
         return
-    graph = graphs.make_graph(args.workload, args.seed)
+    ds = graphs.load_workload(args.workload, args.seed, train_ratio=args.train_ratio)
+    graph = ds.graph
+    ratio = spec["train_ratio"] if args.train_ratio is None else args.train_ratio
     dims = [spec["hidden"], spec["classes"]]
-    ms, cores, epochs = run_cpu(graph, dims, args.steps, args.warmup, budget_s=90.0)
+    warm = max(args.warmup, 3)
+    ms, cores, epochs = run_cpu(graph, dims, args.steps, warm, budget_s=90.0)
     line = {
-        "impl": "reference", "metric": "2-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms, 2),
-        "unit": "ms/epoch", "n_gpus": args.gpus, "steps": epochs, "warmup": min(args.warmup, 2),
+        "impl": "reference", "metric": METRIC, "value": round(ms, 2),
+        "unit": "ms/epoch", "n_gpus": args.gpus, "steps": args.steps, "warmup": warm,
         "ms_per_step": round(ms, 2), "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.workload}: N={graph.num_nodes}, E={graph.num_edges}, dims {dims[0]}/{dims[1]}",
-                   "seed": args.seed, "parallelism": f"{cores} host threads"},
+        "config": {"workload": workload_string(args.workload, spec, graph.num_nodes, graph.num_edges, dims, ratio,
+                                               max(int(ds.avg_degree), 1), args.backsize),
+                   "seed": args.seed, "l2": "inputs exceed L2: each step streams >1 GB of distinct data",
+                   "parallelism": "single GPU",
+                   "kernel": "tiled plan (rows in width classes, padded edge copy)" if args.kernel == "tiles"
+                             else "neighbour-group kernel"},
+        "arm": {"host_threads": cores, "epochs_timed": epochs,
+                "what": "fp32 torch.sparse CSR SpMM on the host cores; four whole-graph aggregations per epoch: "
+                        "the CPU path has no execution-path preparation, so its backward is the uncompacted one "
+                        "(the GPU arm's backward runs over the compacted path)"},
         "cpu_baseline": {"value": round(ms, 2), "unit": "ms/epoch", "cores": cores, "kind": "port",
                          "sample": f"{epochs} epoch(s) of the full workload: 4 torch.sparse CSR SpMMs over the "
                                    f"whole graph (the reference has no CPU implementation of its CUDA operators)"},
         "e2e": {"value": round(ms, 2), "unit": "ms/epoch", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
+    if args.cpu_training_epochs > 0:
+        line["cpu_training"] = {"ms_per_epoch": round(run_cpu_training(ds, spec, args.cpu_training_epochs), 3),
+                                "epochs": args.cpu_training_epochs, "cores": cores,
+                                "what": "whole training epochs on the CPU: forward, loss on the train rows, "
+                                        "backward, Adam (the CPU-only configuration)"}
     print(json.dumps(line), flush=True)
 
 
@@ -453,8 +705,11 @@ def main():
     p.add_argument("--warmup", type=int, default=5)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="rmat21")
+    p.add_argument("--train-ratio", type=float, default=None, help="train mask ratio (default: the workload's own)")
     p.add_argument("--seed", type=int, default=0)
     p.add_argument("--backsize", type=int, default=32)
+    p.add_argument("--kernel", default="tiles", choices=["tiles", "groups"],
+                   help="single GPU: the planned tile kernel the operator module uses, or the stateless group kernel")
     p.add_argument("--exchange", default="balanced_halo", choices=["balanced", "allgather", "halo", "balanced_halo"],
                    help="multi-GPU partition/exchange, see eppgcn_b200.dist.DistHotPath")
     p.add_argument("--chunks", type=int, default=0,
@@ -462,17 +717,25 @@ def main():
                         "every layer is at least 32 columns wide (and splits into 16-byte pieces), else one")
     p.add_argument("--overlap", action="store_true",
                    help="balanced_halo with the push transport and >1 chunk: push chunk c+1 on a side stream while "
-                        "chunk c is aggregated (not yet measured; off by default)")
+                        "chunk c is aggregated")
     p.add_argument("--transport", default="push", choices=["push", "nccl"],
                    help="balanced_halo: peer stores by this library's kernel, or NCCL all-to-all")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-full-epoch", action="store_true")
+    p.add_argument("--no-check", action="store_true")
+    p.add_argument("--no-ref-cuda", action="store_true")
+    p.add_argument("--cpu-training-epochs", type=int, default=0,
+                   help="--impl reference: also time this many whole training epochs on the CPU")
     p.add_argument("--kernels-only", action="store_true",
-                   help="device-resident timing only (no e2e, full-epoch or CPU legs); for profiler captures")
+                   help="device-resident timing only (no check, e2e, full-epoch, reference-kernel or CPU legs); "
+                        "for profiler captures")
+    p.add_argument("--ref-cuda-child", action="store_true", help=argparse.SUPPRESS)
     args = p.parse_args()
     if args.kernels_only:
-        args.no_cpu_baseline = args.no_full_epoch = True
-    if args.impl == "reference":
+        args.no_cpu_baseline = args.no_full_epoch = args.no_check = args.no_ref_cuda = True
+    if args.ref_cuda_child:
+        ref_cuda_child(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_gpu(args)

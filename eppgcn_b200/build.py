@@ -25,7 +25,7 @@ EXT_PATH = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
-LIB_SOURCES = ["spmm.cu", "segment_spmm.cu", "tiled_spmm.cu", "update.cu", "prep.cu", "exchange.cu", "host.cu"]
+LIB_SOURCES = ["spmm.cu", "tiled_spmm.cu", "update.cu", "prep.cu", "exchange.cu", "host.cu"]
 
 
 def _nvcc() -> str:

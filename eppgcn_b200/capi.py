@@ -26,20 +26,14 @@ SIGNATURES = {
     "eppgcn_spmm_forward": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_spmm_backward_compacted": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P]),
     "eppgcn_tile_plan_bytes": (_SZ, [_LL, _I, _I]),
-    "eppgcn_tile_plan_from_csr": (_I, [_P, _P, _SZ, _P, _P, _I, _LL, _I, _I, _P]),
-    "eppgcn_tile_plan_from_ids": (_I, [_P, _P, _SZ, _P, _P, _LL, _I, _I, _I, _P]),
+    "eppgcn_tile_plan_from_csr": (_I, [_P, _P, _SZ, _P, _P, _I, _LL, _I, _P]),
+    "eppgcn_tile_plan_from_ids": (_I, [_P, _P, _SZ, _P, _P, _LL, _I, _I, _P]),
     "eppgcn_pack_scaled_rows": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _I, _P]),
     "eppgcn_tile_plan_destroy": (None, [_P]),
     "eppgcn_tile_plan_info": (_I, [_P, _P]),
     "eppgcn_spmm_tiles": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
-    "eppgcn_segment_plan_bytes": (_SZ, [_LL, _I]),
-    "eppgcn_segment_plan_from_csr": (_I, [_P, _P, _SZ, _P, _I, _LL, _I, _P]),
-    "eppgcn_segment_plan_from_ids": (_I, [_P, _P, _SZ, _P, _LL, _I, _I, _P]),
-    "eppgcn_segment_plan_destroy": (None, [_P]),
-    "eppgcn_segment_plan_info": (_I, [_P, _P]),
-    "eppgcn_spmm_segments": (_I, [_P, _LL, _P, _LL, _P, _P, _P, _I, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
@@ -180,77 +174,16 @@ def spmm_backward_compacted(d_out, ids, part_ptr, edge_list, degrees, num_parts,
     return out
 
 
-class SegmentPlan:
-    """Plan of the chunked aggregation (``eppgcn_segment_plan_*``): where rows
-    start in an edge list.  Owns the device buffer the library writes the plan
-    into and the host handle; both go when the object does."""
-
-    INFO = ("edges", "rows", "chunks", "chunks_per_warp", "nonempty_rows", "cleared_rows", "implicit_row_ids",
-            "clears_whole_result")
-
-    def __init__(self, handle, buf, dim):
-        self._handle, self._buf, self.dim = handle, buf, dim
-        out = (_LL * 8)()
-        check(lib().eppgcn_segment_plan_info(handle, out))
-        self.info = dict(zip(self.INFO, [int(v) for v in out]))
-
-    @staticmethod
-    def _buffer(index, num_edges, num_rows):
-        if not index.is_cuda or index.dtype != torch.int32 or not index.is_contiguous():
-            raise RuntimeError("the plan is built from a contiguous int32 CUDA tensor")
-        nbytes = lib().eppgcn_segment_plan_bytes(int(num_edges), int(num_rows))
-        return torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=index.device), nbytes
-
-    @classmethod
-    def from_csr(cls, row_ptr, num_edges, dim):
-        """Forward plan: row ``r`` owns edges ``[row_ptr[r], row_ptr[r+1])``."""
-        num_rows = row_ptr.numel() - 1
-        buf, nbytes = cls._buffer(row_ptr, num_edges, num_rows)
-        handle = _P()
-        check(lib().eppgcn_segment_plan_from_csr(C.byref(handle), buf.data_ptr(), nbytes, row_ptr.data_ptr(),
-                                                 num_rows, int(num_edges), int(dim), _stream()))
-        return cls(handle, buf, dim)
-
-    @classmethod
-    def from_ids(cls, ids, num_edges, num_rows, dim):
-        """Backward plan: ``ids[e]`` is the (non-decreasing) row of compacted edge ``e < num_edges``."""
-        buf, nbytes = cls._buffer(ids, num_edges, num_rows)
-        handle = _P()
-        check(lib().eppgcn_segment_plan_from_ids(C.byref(handle), buf.data_ptr(), nbytes, ids.data_ptr(),
-                                                 int(num_edges), int(num_rows), int(dim), _stream()))
-        return cls(handle, buf, dim)
-
-    def __del__(self):
-        if getattr(self, "_handle", None) and _lib is not None:
-            _lib.eppgcn_segment_plan_destroy(self._handle)
-            self._handle = None
-
-
-def spmm_segments(src, col_idx, plan, row_scale=None, out=None):
-    """``out[r] = row_scale[r] * sum_e src[col_idx[e]]`` over the rows of ``plan``;
-    ``src`` rows already carry their source-side factor and may be padded."""
-    n = plan.info["rows"]
-    dim = src.size(1)
-    ld = _row_stride(src, "src")
-    if out is None:
-        out = torch.empty(n, dim, device=src.device, dtype=torch.float32)
-    check(lib().eppgcn_spmm_segments(
-        _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), ld,
-        _dev(col_idx, torch.int32, "col_idx"), plan._handle,
-        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, _stream()))
-    return out
-
-
 class TilePlan:
     """Plan of the tiled aggregation (``eppgcn_tile_plan_*``): the rows of an edge
     list sorted into length classes, with the plan's own padded copy of the
     source ids.  Owns the device buffer and the host handle."""
 
-    INFO = ("edges", "rows", "slots", "tiles", "nonempty_rows", "cleared_rows", "atomic_rows",
+    INFO = ("edges", "rows", "slots", "pieces", "nonempty_rows", "cleared_rows", "atomic_rows",
             "clears_whole_result")
 
-    def __init__(self, handle, buf, dim):
-        self._handle, self._buf, self.dim = handle, buf, dim
+    def __init__(self, handle, buf):
+        self._handle, self._buf = handle, buf
         out = (_LL * 8)()
         check(lib().eppgcn_tile_plan_info(handle, out))
         self.info = dict(zip(self.INFO, [int(v) for v in out]))
@@ -261,7 +194,7 @@ class TilePlan:
         return torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=device), nbytes
 
     @classmethod
-    def from_csr(cls, row_ptr, col_idx, dim, num_sources=None):
+    def from_csr(cls, row_ptr, col_idx, num_sources=None):
         """Forward plan: row ``r`` owns edges ``[row_ptr[r], row_ptr[r+1])`` of ``col_idx``;
         ``num_sources`` rows in the source matrix (default: a square graph)."""
         num_rows, num_edges = row_ptr.numel() - 1, col_idx.numel()
@@ -271,19 +204,19 @@ class TilePlan:
         check(lib().eppgcn_tile_plan_from_csr(C.byref(handle), buf.data_ptr(), nbytes,
                                               _dev(row_ptr, torch.int32, "row_ptr"),
                                               _dev(col_idx, torch.int32, "col_idx"), num_rows, num_edges,
-                                              int(num_sources), int(dim), _stream()))
-        return cls(handle, buf, dim)
+                                              int(num_sources), _stream()))
+        return cls(handle, buf)
 
     @classmethod
-    def from_ids(cls, ids, col_idx, num_edges, num_rows, dim, num_sources=None):
+    def from_ids(cls, ids, col_idx, num_edges, num_rows, num_sources=None):
         """Backward plan: ``ids[e]`` is the row and ``col_idx[e]`` the source of compacted edge ``e < num_edges``."""
         num_sources = num_rows if num_sources is None else num_sources
         buf, nbytes = cls._buffer(ids.device, num_edges, num_rows, num_sources)
         handle = _P()
         check(lib().eppgcn_tile_plan_from_ids(C.byref(handle), buf.data_ptr(), nbytes, _dev(ids, torch.int32, "ids"),
                                               _dev(col_idx, torch.int32, "col_idx"), int(num_edges), int(num_rows),
-                                              int(num_sources), int(dim), _stream()))
-        return cls(handle, buf, dim)
+                                              int(num_sources), _stream()))
+        return cls(handle, buf)
 
     def __del__(self):
         if getattr(self, "_handle", None) and _lib is not None:

@@ -18,6 +18,8 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <cstdlib>
+#include <mutex>
 #include <vector>
 
 #include "eppgcn_b200.h"
@@ -45,6 +47,143 @@ struct ScopedTime {
 };
 
 int padded_width(int64_t dim) { return static_cast<int>((dim + 7) / 8 * 8); }
+
+// ---------------------------------------------------------------------------
+// Aggregation plans.  The operators receive the same edge lists epoch after
+// epoch (the CSR for `forward`, the compacted path of a layer for
+// `ours_backward`), so the tile plan of an edge list is prepared at its first
+// use and found again by the identity of the tensors that describe it: data
+// pointers, sizes and in-place modification counters.  A handful of plans is
+// kept (a model has one forward list and one backward list per layer); the
+// least recently used one goes when there are more.
+// EPPGCN_B200_GROUP_KERNEL=1 in the environment turns the plans off: every
+// aggregation then runs the stateless group kernel.
+// ---------------------------------------------------------------------------
+struct PlanKey {
+  const void *a, *b;
+  int64_t na, nb, rows, edges;
+  uint32_t va, vb;
+  int device;
+  bool operator==(const PlanKey &o) const {
+    return a == o.a && b == o.b && na == o.na && nb == o.nb && rows == o.rows && edges == o.edges && va == o.va &&
+           vb == o.vb && device == o.device;
+  }
+};
+
+struct PlanEntry {
+  PlanKey key;
+  eppgcn_tile_plan *plan;
+  torch::Tensor buffer;      // the plan's device arrays
+  torch::Tensor keep_a, keep_b;   // the key's tensors: while they live here their addresses cannot be handed out again
+  uint64_t last_use;
+};
+
+class PlanCache {
+ public:
+  static constexpr size_t kCapacity = 16;
+
+  // Finds the plan of `key`, or builds it with `build(buffer_ptr, buffer_bytes, &plan)`.
+  template <typename Build>
+  const eppgcn_tile_plan *get(const PlanKey &key, const torch::Tensor &key_a, const torch::Tensor &key_b,
+                              int64_t edges, int64_t rows, int64_t sources, Build build) {
+    const auto opts = key_a.options();
+    std::lock_guard<std::mutex> lock(mu_);
+    for (PlanEntry &e : entries_)
+      if (e.key == key) {
+        e.last_use = ++clock_;
+        return e.plan;
+      }
+    const size_t bytes = eppgcn_tile_plan_bytes(edges, static_cast<int>(rows), static_cast<int>(sources));
+    auto buffer = at::empty({static_cast<int64_t>((bytes + 7) / 8)}, opts.dtype(at::kLong));
+    eppgcn_tile_plan *plan = nullptr;
+    epp_check(build(buffer.data_ptr(), bytes, &plan), "eppgcn_tile_plan");
+    if (entries_.size() >= kCapacity) {
+      size_t oldest = 0;
+      for (size_t i = 1; i < entries_.size(); ++i)
+        if (entries_[i].last_use < entries_[oldest].last_use) oldest = i;
+      eppgcn_tile_plan_destroy(entries_[oldest].plan);
+      entries_.erase(entries_.begin() + static_cast<std::ptrdiff_t>(oldest));
+    }
+    entries_.push_back(PlanEntry{key, plan, buffer, key_a, key_b, ++clock_});
+    return plan;
+  }
+
+  void clear() {
+    std::lock_guard<std::mutex> lock(mu_);
+    for (PlanEntry &e : entries_) eppgcn_tile_plan_destroy(e.plan);
+    entries_.clear();
+  }
+
+  size_t size() {
+    std::lock_guard<std::mutex> lock(mu_);
+    return entries_.size();
+  }
+
+ private:
+  std::mutex mu_;
+  std::vector<PlanEntry> entries_;
+  uint64_t clock_ = 0;
+};
+
+// Never destroyed: its tensors must not be released after the CUDA context has gone at exit.
+PlanCache &plan_cache() {
+  static PlanCache *cache = new PlanCache();
+  return *cache;
+}
+
+bool plans_enabled() {
+  const char *v = std::getenv("EPPGCN_B200_GROUP_KERNEL");
+  return !(v && v[0] && v[0] != '0');
+}
+
+const eppgcn_tile_plan *forward_plan(const torch::Tensor &row_pointers, const torch::Tensor &column_index) {
+  const int64_t n = row_pointers.numel() - 1, e = column_index.numel();
+  PlanKey key{row_pointers.data_ptr(), column_index.data_ptr(), row_pointers.numel(), column_index.numel(), n, e,
+              static_cast<uint32_t>(row_pointers._version()), static_cast<uint32_t>(column_index._version()),
+              row_pointers.get_device()};
+  return plan_cache().get(key, row_pointers, column_index, e, n, n, [&](void *buf, size_t bytes, eppgcn_tile_plan **plan) {
+    return eppgcn_tile_plan_from_csr(plan, buf, bytes, row_pointers.data_ptr<int>(), column_index.data_ptr<int>(),
+                                     static_cast<int>(n), e, static_cast<int>(n), current_stream());
+  });
+}
+
+const eppgcn_tile_plan *backward_plan(const torch::Tensor &id, const torch::Tensor &partPointer,
+                                      const torch::Tensor &edgeList, int numParts, int64_t n) {
+  // the path's edge count closes the part pointers; it is read once, when the plan is made
+  PlanKey key{id.data_ptr(), edgeList.data_ptr(), id.numel(), partPointer.numel(), n, numParts,
+              static_cast<uint32_t>(id._version()), static_cast<uint32_t>(edgeList._version()), id.get_device()};
+  return plan_cache().get(key, id, edgeList, id.numel(), n, n, [&](void *buf, size_t bytes, eppgcn_tile_plan **plan) {
+    const int64_t valid = numParts > 0 ? partPointer[numParts].item<int>() : 0;
+    TORCH_CHECK(valid >= 0 && valid <= id.numel() && valid <= edgeList.numel(),
+                "partPointer[numParts] is not an edge count of the compacted lists");
+    return eppgcn_tile_plan_from_ids(plan, buf, bytes, id.data_ptr<int>(), edgeList.data_ptr<int>(), valid,
+                                     static_cast<int>(n), static_cast<int>(n), current_stream());
+  });
+}
+
+// sum over the plan's edges of rows that already carry their source factor; destination factor `degrees`
+torch::Tensor aggregate_planned(const eppgcn_tile_plan *plan, const torch::Tensor &src, const torch::Tensor &degrees,
+                                int64_t n) {
+  const int64_t d = src.size(1);
+  auto out = at::empty({n, d}, src.options());
+  if (n == 0) return out;
+  epp_check(eppgcn_spmm_tiles(out.data_ptr<float>(), 0, src.data_ptr<float>(), src.stride(0), plan,
+                              degrees.data_ptr<float>(), static_cast<int>(d), current_stream()),
+            "eppgcn_spmm_tiles");
+  return out;
+}
+
+// degrees[r] * x[r] for the rows the plan's edges name, in rows padded to 32 bytes
+torch::Tensor pack_scaled(const eppgcn_tile_plan *plan, const torch::Tensor &x, const torch::Tensor &degrees) {
+  const int64_t n = x.size(0), d = x.size(1), ld = padded_width(d);
+  auto full = at::empty({n, ld}, x.options());
+  if (n > 0)
+    epp_check(eppgcn_pack_scaled_rows(full.data_ptr<float>(), ld, x.data_ptr<float>(), x.stride(0),
+                                      degrees.data_ptr<float>(), plan, static_cast<int>(n), static_cast<int>(d),
+                                      current_stream()),
+              "eppgcn_pack_scaled_rows");
+  return full.narrow(1, 0, d);
+}
 
 // diag(degrees) * (X @ W), written into rows whose stride is a multiple of 32
 // bytes, so every gathered row starts on a sector boundary and can be fetched
@@ -138,6 +277,8 @@ std::vector<torch::Tensor> spmm_forward(torch::Tensor input, torch::Tensor weigh
     tmp = update_scaled_padded(input, weight, degrees);
   }
   ScopedTime t(0);
+  if (plans_enabled() && input.size(0) > 0 && row_pointers.numel() == input.size(0) + 1)
+    return {aggregate_planned(forward_plan(row_pointers, column_index), tmp, degrees, input.size(0))};
   return {aggregate_forward(tmp, row_pointers, column_index, degrees, part_pointers, part2Node, partSize,
                             dimWorker, warpPerBlock, /*prescaled=*/true)};
 }
@@ -158,8 +299,13 @@ std::vector<torch::Tensor> spmm_backward(torch::Tensor d_output, torch::Tensor X
   torch::Tensor d_input_prime;
   {
     ScopedTime t(2, 0);
-    d_input_prime = aggregate_forward(d_output, row_pointers, column_index, degrees, part_pointers, part2Node,
-                                      partSize, dimWorker, warpPerBlock);
+    if (plans_enabled() && d_output.size(0) > 0 && row_pointers.numel() == d_output.size(0) + 1) {
+      const eppgcn_tile_plan *plan = forward_plan(row_pointers, column_index);
+      d_input_prime = aggregate_planned(plan, pack_scaled(plan, d_output, degrees), degrees, d_output.size(0));
+    } else {
+      d_input_prime = aggregate_forward(d_output, row_pointers, column_index, degrees, part_pointers, part2Node,
+                                        partSize, dimWorker, warpPerBlock);
+    }
   }
   ScopedTime t(3);
   return backward_update(d_input_prime, X, W);
@@ -207,8 +353,13 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
               "partPointer must hold numParts + 1 entries");
   c10::cuda::CUDAGuard guard(d_output.device());
   const int64_t n = d_output.size(0), d = d_output.size(1);
-  auto d_input_prime = at::empty({n, d}, d_output.options());
-  {
+  torch::Tensor d_input_prime;
+  if (plans_enabled() && n > 0) {
+    ScopedTime t(2, layer);
+    const eppgcn_tile_plan *plan = backward_plan(id, partPointer, edgeList, numParts, n);
+    d_input_prime = aggregate_planned(plan, pack_scaled(plan, d_output, degrees), degrees, n);
+  } else {
+    d_input_prime = at::empty({n, d}, d_output.options());
     ScopedTime t(2, layer);
     epp_check(eppgcn_spmm_backward_compacted(d_input_prime.data_ptr<float>(), 0, d_output.data_ptr<float>(), d,
                                              id.data_ptr<int>(), partPointer.data_ptr<int>(),
@@ -371,6 +522,10 @@ torch::Tensor get_ginfo(torch::Tensor node_deg, int valid_len) {
   return re;
 }
 
+// Extras beside the reference's twelve functions: the plans the operators keep.
+void clear_plans() { plan_cache().clear(); }
+int64_t num_plans() { return static_cast<int64_t>(plan_cache().size()); }
+
 void print_time() { epp_check(eppgcn_print_time(), "eppgcn_print_time"); }
 void clear_time() { epp_check(eppgcn_clear_time(), "eppgcn_clear_time"); }
 
@@ -389,4 +544,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("get_map_back_part_size", &get_map_back_part_size, "regression rule for the backward part size (CUDA)");
   m.def("split_back_part", &split_back_part, "split active rows into backward parts (CUDA)");
   m.def("get_ginfo", &get_ginfo, "degree histogram features (CPU)");
+  m.def("clear_plans", &clear_plans, "drop the aggregation plans the operators keep (not in the reference)");
+  m.def("num_plans", &num_plans, "number of aggregation plans currently kept (not in the reference)");
 }

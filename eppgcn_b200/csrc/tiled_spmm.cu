@@ -13,9 +13,9 @@
 // by one group of lanes and stored exactly once: the result matrix is not
 // zero-filled and written again.
 //
-// Work unit.  A "sub-warp" of LPR lanes (four columns per lane, so 4 / 8 / 16 /
-// 32 lanes for rows of up to 16 / 32 / 64 / 128 columns) owns one row of the
-// current class, a warp owns 32/LPR consecutive rows of that class ("a tile"),
+// Work unit.  A "sub-warp" of L = ceil(columns / 4) lanes (four columns per
+// lane: 4 lanes for 16 columns, 6 for 22, 16 for 64 ...) owns one row of the
+// current class, a warp owns floor(32 / L) consecutive rows of that class ("a tile"),
 // and tiles are dealt to the persistent warps in descending class order.  All
 // sub-warps of a warp therefore run the same number of batches of eight
 // independent 16-byte row loads, close their rows at the same instruction, and
@@ -44,12 +44,17 @@ constexpr unsigned kAtomicBit = 0x80000000u;    // in a rank's row id: the piece
 #ifndef EPP_TILE_MINB
 #define EPP_TILE_MINB 3
 #endif
+// Rank count of a class is a multiple of this (times 8 in the narrow classes, where a sub-warp
+// takes up to 8 rows): divisible by every rows-per-tile value floor(32 / L), L = 1..32.
+constexpr int kRankPad = 480;
 constexpr int kTileThreads = EPP_TILE_THREADS;
 constexpr int kTileMinBlocks = EPP_TILE_MINB;
 
 // Classes in processing order (widest first).  Class k covers ranks
 // [rank_off[k], rank_off[k+1]) and slots [slot_off[k], slot_off[k+1]); a rank
-// owns width[k] consecutive slots; tile_begin[k] is the index of its first tile.
+// owns width[k] consecutive slots.  tile_begin[k], the index of the class's
+// first tile, depends on the rows per tile and is filled in per launch; the
+// rank counts are padded so that every tile shape divides them.
 struct ClassTable {
   int count;
   int width[kMaxClasses];
@@ -72,7 +77,7 @@ struct eppgcn_tile_plan {
   // host side
   epp::ClassTable table;
   long long num_edges, num_slots;
-  int num_rows, num_sources, num_ranks, num_tiles, num_zero, zero_all, lanes, nonempty_rows, hub_rows;
+  int num_rows, num_sources, num_ranks, num_zero, zero_all, nonempty_rows, hub_rows;
 };
 
 namespace epp {
@@ -88,6 +93,7 @@ struct TileArgs {
   const float *row_scale;         // destination-side factor per row id, or NULL
   int num_tiles;
   int dim;                        // columns handled by this launch
+  int lanes;                      // lanes per row, ceil(dim / 4)
   ClassTable t;
 };
 
@@ -122,8 +128,7 @@ struct TilePos {
   int rank;
   long long slot;
 };
-template <int G>
-__device__ __forceinline__ TilePos locate(const ClassTable &t, int tile, int sub, int &k) {
+__device__ __forceinline__ TilePos locate(const ClassTable &t, int G, int tile, int sub, int &k) {
   while (k + 1 < t.count && tile >= t.tile_begin[k + 1]) ++k;
   const int w = t.width[k];
   const int per_sub = w >= 8 ? 1 : 8 / w;                    // rows of one sub-warp in this tile
@@ -135,13 +140,15 @@ __device__ __forceinline__ TilePos locate(const ClassTable &t, int tile, int sub
   return p;
 }
 
-template <int LPR, int OV>
+template <int OV>
 __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kernel(const TileArgs a) {
-  constexpr int G = kWarp / LPR;               // rows (of the wide classes) per tile
+  const int G = kWarp / a.lanes;               // rows (of the wide classes) per tile
   const int lane = threadIdx.x & 31;
-  const int sub = lane / LPR;
-  const int fcol = (lane % LPR) * 4;
-  const bool has_cols = fcol < a.dim;
+  // lanes beyond the last whole sub-warp (32 is not a multiple of 6, say) shadow the last row and never store
+  const bool spare = lane >= G * a.lanes;
+  const int sub = spare ? G - 1 : lane / a.lanes;
+  const int fcol = spare ? 0 : (lane % a.lanes) * 4;
+  const bool has_cols = !spare && fcol < a.dim;
   const int n = min(4, a.dim - fcol);          // columns of this lane that exist
   // lanes without columns read column 0 and never store
   const char *glane = reinterpret_cast<const char *>(a.src + (has_cols ? fcol : 0));
@@ -154,7 +161,7 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kerne
   if (tile >= a.num_tiles) return;
 
   int k = 0;
-  TilePos pos = locate<G>(a.t, tile, sub, k);
+  TilePos pos = locate(a.t, G, tile, sub, k);
   int c[8];
   load8(a.slots + pos.slot, c);
   int rid_wide = pos.width >= 8 ? __ldg(a.row_of + pos.rank) : -1;
@@ -164,7 +171,7 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kerne
     const int next = tile + stride;
     TilePos npos = pos;
     int kn = k;
-    if (next < a.num_tiles) npos = locate<G>(a.t, next, sub, kn);
+    if (next < a.num_tiles) npos = locate(a.t, G, next, sub, kn);
     int cn[8];
     int rid_next = -1;
     float4 v[8];
@@ -320,10 +327,8 @@ __global__ void __launch_bounds__(256) pack_scaled_rows_kernel(float *dst, long 
 }
 
 int lanes_for_dim(int dim) {            // lanes per row: four columns per lane, at most 128 columns per launch
-  if (dim <= 16) return 4;
-  if (dim <= 32) return 8;
-  if (dim <= 64) return 16;
-  return 32;
+  const int l = (dim + 3) / 4;
+  return l > 32 ? 32 : l;
 }
 
 // Class of a row (or of the remainder piece of a hub row) with `len` edges, as
@@ -346,9 +351,9 @@ PlanBounds plan_bounds(long long num_edges, int num_rows) {
   const size_t rows_with_edges = static_cast<size_t>(std::min<long long>(num_rows, num_edges));
   PlanBounds b;
   // a rank is padded by at most 7 slots; every class ends with at most one tile of padding ranks
-  b.ranks = rows_with_edges + static_cast<size_t>(num_edges / kPieceEdges) + kNumClasses * 8 * 8 + 64;
+  b.ranks = rows_with_edges + static_cast<size_t>(num_edges / kPieceEdges) + kNumClasses * 8 * kRankPad + 64;
   b.slots = static_cast<size_t>(num_edges) + 7 * (rows_with_edges + static_cast<size_t>(num_edges / kPieceEdges)) +
-            static_cast<size_t>(kNumClasses) * 8 * 8 * kPieceEdges + 64;
+            static_cast<size_t>(kRankPad) * (64 + 56 + 48 + 40 + 32 + 24 + 16 + 8 + 8 * (4 + 2 + 1)) + 64;
   return b;
 }
 struct PlanLayout {
@@ -376,7 +381,7 @@ struct Segment {
 // the edge list.  Host work is linear in the number of rows; the padded slot
 // array is filled on the device.
 int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, const std::vector<Segment> &segs,
-               const int *col_dev, long long num_edges, int num_rows, int num_sources, int dim, cudaStream_t s) {
+               const int *col_dev, long long num_edges, int num_rows, int num_sources, cudaStream_t s) {
   const PlanLayout l = plan_layout(num_edges, num_rows, num_sources);
   if (dev_bytes < l.total) {
     set_error("plan buffer too small: %zu bytes given, %zu needed", dev_bytes, l.total);
@@ -397,8 +402,6 @@ int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, con
   p->num_edges = num_edges;
   p->num_rows = num_rows;
   p->num_sources = num_sources;
-  p->lanes = lanes_for_dim(dim > 128 ? 128 : dim);
-  const int G = kWarp / p->lanes;
 
   // ranks per class: hub rows contribute their 64-edge pieces to class 0 and their remainder to its own class
   long long count[kNumClasses] = {0};
@@ -412,42 +415,40 @@ int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, con
   }
   ClassTable &t = p->table;
   t.count = 0;
-  long long rank_off = 0, slot_off = 0, tile_off = 0;
+  long long rank_off = 0, slot_off = 0;
   int slot_of_class[kNumClasses];
   long long next_rank[kNumClasses];
   for (int k = 0; k < kNumClasses; ++k) {
     slot_of_class[k] = -1;
     if (!count[k]) continue;
     const int w = class_width(k);
-    const int per_tile = G * (w >= 8 ? 1 : 8 / w);                     // ranks per tile
-    const long long tiles = (count[k] + per_tile - 1) / per_tile;
+    const long long pad = w >= 8 ? kRankPad : 8 * kRankPad;            // every tile shape divides it
+    const long long ranks = (count[k] + pad - 1) / pad * pad;
     const int idx = t.count++;
     slot_of_class[k] = idx;
     t.width[idx] = w;
-    t.tile_begin[idx] = static_cast<int>(tile_off);
+    t.tile_begin[idx] = 0;
     t.rank_off[idx] = static_cast<int>(rank_off);
     t.slot_off[idx] = slot_off;
     next_rank[k] = rank_off;
-    rank_off += tiles * per_tile;
-    slot_off += tiles * per_tile * w;
-    tile_off += tiles;
+    rank_off += ranks;
+    slot_off += ranks * w;
   }
   for (int i = t.count; i <= kMaxClasses; ++i) {
-    t.tile_begin[i] = static_cast<int>(tile_off);
+    t.tile_begin[i] = 0;
     t.rank_off[i] = static_cast<int>(rank_off);
     t.slot_off[i] = slot_off;
     if (i < kMaxClasses) t.width[i] = 1;
   }
   const PlanBounds bound = plan_bounds(num_edges, num_rows);
   if (static_cast<size_t>(rank_off) > bound.ranks || static_cast<size_t>(slot_off) > bound.slots ||
-      tile_off >= (1LL << 31)) {
+      rank_off >= (1LL << 31)) {
     delete p;
     set_error("plan exceeds its size bound (%lld ranks, %lld slots)", rank_off, slot_off);
     return EPP_ERR_TOO_LARGE;
   }
   p->num_ranks = static_cast<int>(rank_off);
   p->num_slots = slot_off;
-  p->num_tiles = static_cast<int>(tile_off);
 
   std::vector<int> row_of(static_cast<size_t>(rank_off), -1), seg_start(static_cast<size_t>(rank_off), 0),
       seg_len(static_cast<size_t>(rank_off), 0);
@@ -503,23 +504,26 @@ int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, con
   return EPP_OK;
 }
 
-template <int LPR, int OV>
-int launch_tiles(const TileArgs &a, cudaStream_t s) {
+template <int OV>
+int launch_tiles(TileArgs &a, cudaStream_t s) {
   int num_sms = 0;
   if (const int rc = device_sm_count(&num_sms); rc != EPP_OK) return rc;
-  long long blocks = ceil_div_ll(a.num_tiles, kTileThreads / kWarp);
+  // tiles of this launch's shape: floor(32 / lanes) rows per tile (times 8, 4, 2 in the narrow classes)
+  const int G = kWarp / a.lanes;
+  long long tiles = 0;
+  for (int k = 0; k < a.t.count; ++k) {
+    const int w = a.t.width[k];
+    a.t.tile_begin[k] = static_cast<int>(tiles);
+    tiles += (a.t.rank_off[k + 1] - a.t.rank_off[k]) / (G * (w >= 8 ? 1 : 8 / w));
+  }
+  for (int k = a.t.count; k <= kMaxClasses; ++k) a.t.tile_begin[k] = static_cast<int>(tiles);
+  a.num_tiles = static_cast<int>(tiles);
+  long long blocks = ceil_div_ll(tiles, kTileThreads / kWarp);
   const long long cap = static_cast<long long>(num_sms) * kTileMinBlocks;
   if (blocks > cap) blocks = cap;
-  tiled_spmm_kernel<LPR, OV><<<static_cast<unsigned>(blocks), kTileThreads, 0, s>>>(a);
+  tiled_spmm_kernel<OV><<<static_cast<unsigned>(blocks), kTileThreads, 0, s>>>(a);
   EPP_CHECK_LAUNCH("tiled_spmm_kernel");
   return EPP_OK;
-}
-
-template <int LPR>
-int launch_by_store(const TileArgs &a, int ovec, cudaStream_t s) {
-  if (ovec == 4) return launch_tiles<LPR, 4>(a, s);
-  if (ovec == 2) return launch_tiles<LPR, 2>(a, s);
-  return launch_tiles<LPR, 1>(a, s);
 }
 
 }  // namespace
@@ -534,9 +538,9 @@ EPP_EXPORT size_t eppgcn_tile_plan_bytes(long long num_edges, int num_rows, int 
 
 EPP_EXPORT int eppgcn_tile_plan_from_csr(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
                                          const int *row_ptr, const int *col_idx, int num_rows, long long num_edges,
-                                         int num_sources, int dim, void *stream) {
+                                         int num_sources, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  EPP_REQUIRE(plan && dev_buf && num_rows >= 0 && num_edges >= 0 && num_sources >= 0 && dim >= 1, "bad argument");
+  EPP_REQUIRE(plan && dev_buf && num_rows >= 0 && num_edges >= 0 && num_sources >= 0, "bad argument");
   EPP_REQUIRE(num_edges < (1LL << 31), "edge count exceeds int32");
   EPP_REQUIRE(reinterpret_cast<uintptr_t>(dev_buf) % 256 == 0, "plan buffer must be 256-byte aligned");
   EPP_REQUIRE(num_rows == 0 || row_ptr, "null pointer");
@@ -553,14 +557,14 @@ EPP_EXPORT int eppgcn_tile_plan_from_csr(eppgcn_tile_plan **plan, void *dev_buf,
     EPP_REQUIRE(beg >= 0 && end >= beg && end <= num_edges, "row_ptr is not a non-decreasing offset array");
     if (end > beg) segs.push_back({r, beg, end - beg});
   }
-  return build_plan(plan, dev_buf, dev_bytes, segs, col_idx, num_edges, num_rows, num_sources, dim, s);
+  return build_plan(plan, dev_buf, dev_bytes, segs, col_idx, num_edges, num_rows, num_sources, s);
 }
 
 EPP_EXPORT int eppgcn_tile_plan_from_ids(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
                                          const int *ids, const int *col_idx, long long num_edges, int num_rows,
-                                         int num_sources, int dim, void *stream) {
+                                         int num_sources, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  EPP_REQUIRE(plan && dev_buf && num_rows >= 0 && num_edges >= 0 && num_sources >= 0 && dim >= 1, "bad argument");
+  EPP_REQUIRE(plan && dev_buf && num_rows >= 0 && num_edges >= 0 && num_sources >= 0, "bad argument");
   EPP_REQUIRE(num_edges < (1LL << 31), "edge count exceeds int32");
   EPP_REQUIRE(reinterpret_cast<uintptr_t>(dev_buf) % 256 == 0, "plan buffer must be 256-byte aligned");
   EPP_REQUIRE(num_edges == 0 || (ids && col_idx), "null pointer");
@@ -581,7 +585,7 @@ EPP_EXPORT int eppgcn_tile_plan_from_ids(eppgcn_tile_plan **plan, void *dev_buf,
     segs.push_back({r, static_cast<int>(e), static_cast<int>(f - e)});
     e = f;
   }
-  return build_plan(plan, dev_buf, dev_bytes, segs, col_idx, num_edges, num_rows, num_sources, dim, s);
+  return build_plan(plan, dev_buf, dev_bytes, segs, col_idx, num_edges, num_rows, num_sources, s);
 }
 
 EPP_EXPORT int eppgcn_pack_scaled_rows(float *dst, long long dst_ld, const float *x, long long ldx,
@@ -614,7 +618,7 @@ EPP_EXPORT void eppgcn_tile_plan_destroy(eppgcn_tile_plan *plan) { delete plan; 
 
 EPP_EXPORT int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *out8) {
   EPP_REQUIRE(plan && out8, "null pointer");
-  out8[0] = plan->num_edges; out8[1] = plan->num_rows; out8[2] = plan->num_slots; out8[3] = plan->num_tiles;
+  out8[0] = plan->num_edges; out8[1] = plan->num_rows; out8[2] = plan->num_slots; out8[3] = plan->num_ranks;
   out8[4] = plan->nonempty_rows; out8[5] = plan->num_zero; out8[6] = plan->hub_rows; out8[7] = plan->zero_all;
   return EPP_OK;
 }
@@ -629,8 +633,6 @@ EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src,
   if (n == 0) return EPP_OK;
   EPP_REQUIRE(out, "null pointer");
   if (out_ld == 0) out_ld = dim;
-  EPP_REQUIRE(lanes_for_dim(dim > 128 ? 128 : dim) == plan->lanes,
-              "the plan was prepared for another row width class (<= 16, <= 32, <= 64, wider)");
   int ovec = 1;
   if (out_ld % 4 == 0 && aligned(out, 16)) ovec = 4;
   else if (out_ld % 2 == 0 && aligned(out, 8)) ovec = 2;
@@ -649,7 +651,7 @@ EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src,
     else zero_listed_rows_kernel<1><<<g, 256, 0, s>>>(out, out_ld, dim, plan->zero_rows, plan->num_zero);
     EPP_CHECK_LAUNCH("zero_listed_rows_kernel");
   }
-  if (plan->num_tiles == 0) return EPP_OK;
+  if (plan->num_ranks == 0) return EPP_OK;
   EPP_REQUIRE(src, "null pointer");
   EPP_REQUIRE(src_ld % 4 == 0 && src_ld >= (dim + 3) / 4 * 4 && src_ld <= 0x3fffffffLL && aligned(src, 16),
               "source rows must be 16-byte aligned and padded to a multiple of 4 floats");
@@ -657,12 +659,8 @@ EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src,
     TileArgs a{};
     a.out = out + col0; a.out_ld = out_ld; a.src = src + col0; a.src_ld = src_ld;
     a.slots = plan->slots; a.row_of = plan->row_of; a.row_scale = row_scale;
-    a.num_tiles = plan->num_tiles; a.dim = dim - col0 < 128 ? dim - col0 : 128; a.t = plan->table;
-    int rc;
-    if (plan->lanes == 4) rc = launch_by_store<4>(a, ovec, s);
-    else if (plan->lanes == 8) rc = launch_by_store<8>(a, ovec, s);
-    else if (plan->lanes == 16) rc = launch_by_store<16>(a, ovec, s);
-    else rc = launch_by_store<32>(a, ovec, s);
+    a.dim = dim - col0 < 128 ? dim - col0 : 128; a.lanes = lanes_for_dim(a.dim); a.t = plan->table;
+    const int rc = ovec == 4 ? launch_tiles<4>(a, s) : ovec == 2 ? launch_tiles<2>(a, s) : launch_tiles<1>(a, s);
     if (rc != EPP_OK) return rc;
   }
   return EPP_OK;

@@ -104,59 +104,14 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
  * Planned aggregation: the same sums as eppgcn_spmm_forward (called with
  * deg_col == NULL) and eppgcn_spmm_backward_compacted, i.e. the work of
  * spmm_forward_cuda_kernel / ours_backward_cuda_kernel
- * (EPPGCN/GCNConv/EPPGCN_kernel.cu:204-295, :626-670), computed over fixed
- * chunks of 64 edges from a plan that is prepared once per edge list.  The
- * reference has no such object; it replaces the per-call zero-fill
- * (EPPGCN_kernel.cu:150, :562) and the per-group atomics (:289-293, :666-668):
- * the result is written once, rows are summed with atomics only where they
- * cross the span of edges one warp works on (64 edges per group of lanes
- * that covers a row).
- *
- *   out[r][:] = row_scale[r] * sum over edges e of row r:  src[col_idx[e]][:]
- *
- * A plan describes where rows start in the edge list.  It is built from
- *   - a CSR row pointer (forward: row r owns edges [row_ptr[r], row_ptr[r+1])), or
- *   - a row id per edge, non-decreasing (backward: the `ids` array that
- *     eppgcn_compact_mask produced, valid prefix only).
- * eppgcn_segment_plan_bytes gives the size of the device buffer the caller
- * supplies (256-byte aligned; it must outlive the plan); the builder enqueues
- * a few small kernels on `stream` and synchronises that stream once to read
- * two counts back.  The plan handle itself is a small host object, freed by
- * eppgcn_segment_plan_destroy.  `dim` selects the row-width class the plan
- * serves (<= 16 columns, <= 32, <= 64, wider): eppgcn_spmm_segments rejects a plan
- * of another class.  eppgcn_segment_plan_info: out8 = {edges, rows, chunks,
- * chunks per warp, non-empty rows, rows cleared per call, row ids implicit,
- * whole result cleared per call}.
- *
- * eppgcn_spmm_segments:
- * out       rows of out_ld floats (0 = dense [rows][dim]); columns 0..dim-1 of
- *           every row are written (rows without edges come back zero).
- * src       source rows, already multiplied by their source-side factor
- *           (eppgcn_update_scaled does that for the forward); row stride
- *           src_ld a multiple of 4 floats, base 16-byte aligned.
- * col_idx   the edge list's source row per edge (positions into src),
- *           16-byte aligned.
- * row_scale destination-side factor per row id, or NULL for 1.
- */
-typedef struct eppgcn_segment_plan eppgcn_segment_plan;
-size_t eppgcn_segment_plan_bytes(long long num_edges, int num_rows);
-int eppgcn_segment_plan_from_csr(eppgcn_segment_plan **plan, void *dev_buf, size_t dev_bytes,
-                                 const int *row_ptr, int num_rows, long long num_edges, int dim,
-                                 void *stream);
-int eppgcn_segment_plan_from_ids(eppgcn_segment_plan **plan, void *dev_buf, size_t dev_bytes,
-                                 const int *ids, long long num_edges, int num_rows, int dim,
-                                 void *stream);
-void eppgcn_segment_plan_destroy(eppgcn_segment_plan *plan);
-int eppgcn_segment_plan_info(const eppgcn_segment_plan *plan, long long *out8);
-int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long long src_ld,
-                         const int *col_idx, const eppgcn_segment_plan *plan, const float *row_scale,
-                         int dim, void *stream);
-
-/* ------------------------------------------------------------------------
- * Tiled planned aggregation (see eppgcn_spmm_segments for what is computed and
- * which reference code it stands in for): the plan re-orders the rows by their
+ * (EPPGCN/GCNConv/EPPGCN_kernel.cu:204-295, :626-670), from a plan that is
+ * prepared once per edge list.  The reference has no such object; the plan
+ * replaces the per-call zero-fill (EPPGCN_kernel.cu:150, :562) and the
+ * per-group atomics (:289-293, :666-668): it re-orders the rows by their
  * number of edges and keeps its own padded copy of the edge list, so that the
- * lanes of a warp always work on rows of one length class.
+ * lanes of a warp always work on rows of one length class, every row of up to
+ * 64 edges is stored exactly once, and only longer rows are cleared first and
+ * summed with vector atomics.
  *
  *   out[r][:] = row_scale[r] * sum over edges e of row r:  src[col_idx[e]][:]
  *
@@ -168,14 +123,20 @@ int eppgcn_spmm_segments(float *out, long long out_ld, const float *src, long lo
  * fills the padded edge copy on the device and synchronises `stream`.  The
  * device buffer (eppgcn_tile_plan_bytes, 256-byte aligned) must outlive the
  * plan; col_idx, row_ptr and ids are not needed after the build.
- * `dim` selects the row-width class (<= 16 columns, <= 32, <= 64, wider) as for
- * the segment plan.  eppgcn_tile_plan_info: out8 = {edges, rows, padded edge
- * slots, tiles, non-empty rows, rows cleared per call, rows summed with atomics
- * (more than 64 edges), whole result cleared per call}.
+ * One plan serves every row width.  eppgcn_tile_plan_info: out8 = {edges, rows,
+ * padded edge slots, padded row pieces, non-empty rows, rows cleared per call,
+ * rows summed with atomics (more than 64 edges), whole result cleared per call}.
  * num_sources is the number of rows of the source matrix (col_idx values are
  * below it; num_rows for a square graph); the plan remembers which of them an
  * edge names.
- * eppgcn_spmm_tiles: arguments as eppgcn_spmm_segments, minus col_idx.
+ * eppgcn_spmm_tiles:
+ * out       rows of out_ld floats (0 = dense [rows][dim]); columns 0..dim-1 of
+ *           every row are written (rows without edges come back zero).
+ * src       source rows, already multiplied by their source-side factor
+ *           (eppgcn_update_scaled does that for the forward,
+ *           eppgcn_pack_scaled_rows for the backward); row stride src_ld a
+ *           multiple of 4 floats, base 16-byte aligned.
+ * row_scale destination-side factor per row id, or NULL for 1.
  *
  * eppgcn_pack_scaled_rows prepares the source of a backward aggregation, in
  * place of the per-edge degrees[...] factor of ours_backward_cuda_kernel
@@ -188,10 +149,10 @@ typedef struct eppgcn_tile_plan eppgcn_tile_plan;
 size_t eppgcn_tile_plan_bytes(long long num_edges, int num_rows, int num_sources);
 int eppgcn_tile_plan_from_csr(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
                               const int *row_ptr, const int *col_idx, int num_rows, long long num_edges,
-                              int num_sources, int dim, void *stream);
+                              int num_sources, void *stream);
 int eppgcn_tile_plan_from_ids(eppgcn_tile_plan **plan, void *dev_buf, size_t dev_bytes,
                               const int *ids, const int *col_idx, long long num_edges, int num_rows,
-                              int num_sources, int dim, void *stream);
+                              int num_sources, void *stream);
 void eppgcn_tile_plan_destroy(eppgcn_tile_plan *plan);
 int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *out8);
 int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src, long long src_ld,

@@ -343,6 +343,30 @@ def ours_backward_aggregate_loops(ids, part_pointer, edge_list, degrees, d_out, 
     return out
 
 
+def spmm_rows(indptr, indices, rows, feat, row_scale=None):
+    """The aggregation of selected rows only, in float64: ``out[i] = row_scale[rows[i]] * sum of
+    feat[c] over the edges (rows[i], c)``.  ``feat`` rows carry whatever source-side factor the
+    caller folded in.  Same sums as EPPGCN_kernel.cu:263-293 for a subset of the rows; lets a
+    checker look at a sample of a graph that is too large for the full product."""
+    n = len(indptr) - 1
+    a = sp.csr_matrix((np.ones(len(indices), dtype=np.float64), indices, indptr), shape=(n, feat.shape[0]))
+    out = a[np.asarray(rows)] @ np.asarray(feat, dtype=np.float64)
+    if row_scale is not None:
+        out = out * np.asarray(row_scale, dtype=np.float64)[np.asarray(rows)][:, None]
+    return out
+
+
+def spmm_rows_from_pairs(row_ids, cols, num_rows, rows, feat, row_scale=None):
+    """As :func:`spmm_rows` for an edge list given as (row id, source) pairs -- the compacted path
+    ``(id[e], edgeList[e])`` of EPPGCN_kernel.cu:654-668 -- instead of a CSR."""
+    a = sp.coo_matrix((np.ones(len(cols), dtype=np.float64), (np.asarray(row_ids), np.asarray(cols))),
+                      shape=(num_rows, feat.shape[0])).tocsr()
+    out = a[np.asarray(rows)] @ np.asarray(feat, dtype=np.float64)
+    if row_scale is not None:
+        out = out * np.asarray(row_scale, dtype=np.float64)[np.asarray(rows)][:, None]
+    return out
+
+
 def gcn_layer_forward(x, w, indptr, indices, degrees):
     """Whole ``forward`` operator (EPPGCN_kernel.cu:142-184) in float64."""
     return spmm_forward(indptr, indices, degrees,

@@ -2,7 +2,7 @@
 and the 1.13-million-vertex social-shaped graph at train ratios 0.01 / 0.1 /
 0.5.  Preparation (mask -> compaction -> splitting) is compared bit for bit
 with the vectorised numpy oracle on the full arrays; the forward and the
-compacted backward aggregation of both kernels (group kernel, planned kernel)
+compacted backward aggregation of both kernels (group kernel, tiled planned kernel)
 are compared with the float64 oracle on every row.
 Tolerance: |got - want| <= 1e-6 + 1e-5*|want|; twice that where the source rows
 were scaled in fp32 before the sum (pre-scaled rows)."""
@@ -82,10 +82,7 @@ def test_forward_aggregation_matches_float64_on_every_row(prepared, cuda, dim):
     assert_close(got.cpu().numpy(), want, 2e-5, 2e-6, what=f"group kernel, pre-scaled rows, forward dim {dim}")
     src = torch.zeros(n, ld, device=cuda)[:, :dim]
     src.copy_(scaled)
-    plan = capi.SegmentPlan.from_csr(P["row"], P["e"], dim)
-    got = capi.spmm_segments(src, P["col"], plan, P["degd"])
-    assert_close(got.cpu().numpy(), want, 2e-5, 2e-6, what=f"planned kernel, forward dim {dim}")
-    got = capi.spmm_tiles(src, capi.TilePlan.from_csr(P["row"], P["col"], dim), P["degd"])
+    got = capi.spmm_tiles(src, capi.TilePlan.from_csr(P["row"], P["col"]), P["degd"])
     assert_close(got.cpu().numpy(), want, 2e-5, 2e-6, what=f"tiled kernel, forward dim {dim}")
 
 
@@ -103,12 +100,7 @@ def test_compacted_backward_matches_float64_on_every_row(prepared, cuda, conv, d
     ld = (dim + 7) // 8 * 8
     src = torch.zeros(n, ld, device=cuda)[:, :dim]
     src.copy_(dd * P["degd"][:, None])
-    plan = capi.SegmentPlan.from_ids(p["id"], p["valid"], n, dim)
-    got = capi.spmm_segments(src, p["edges"], plan, P["degd"])
-    got = got.cpu().numpy()
-    assert_close(got, want, 2e-5, 2e-6, what=f"planned kernel, backward conv {conv + 1}")
-    assert np.all(got[w["node_degs"] == 0] == 0), "rows off the path must come back zero"
-    got = capi.spmm_tiles(src, capi.TilePlan.from_ids(p["id"], p["edges"], p["valid"], n, dim), P["degd"])
+    got = capi.spmm_tiles(src, capi.TilePlan.from_ids(p["id"], p["edges"], p["valid"], n), P["degd"])
     got = got.cpu().numpy()
     assert_close(got, want, 2e-5, 2e-6, what=f"tiled kernel, backward conv {conv + 1}")
     assert np.all(got[w["node_degs"] == 0] == 0), "rows off the path must come back zero"

@@ -9,12 +9,42 @@ import torch
 from eppgcn_b200 import capi
 from oracle import epp_oracle as O
 from tests.helpers import assert_close, degrees_of, random_csr, t
-from tests.test_gpu_segments import GRAPHS, make_path, padded_rows
 
 pytestmark = pytest.mark.gpu
 
+GRAPHS = {
+    "tiny":    dict(n=9, avg_deg=2.0, seed=1, empty_frac=0.3),
+    "sparse":  dict(n=300, avg_deg=3.0, seed=2, empty_frac=0.2),
+    "hubs":    dict(n=700, avg_deg=6.0, seed=3, hubs=3, hub_deg=650),
+    "dense":   dict(n=128, avg_deg=40.0, seed=4),
+    "loops":   dict(n=2000, avg_deg=1.0, seed=5, empty_frac=0.5),
+    "chunk64": dict(n=400, avg_deg=64.0, seed=7),
+}
+
+
+def padded_rows(a, cuda, pad_to=4, poison=True):
+    """[n, d] view of a buffer whose row stride is d rounded up to `pad_to` floats; the padding is NaN
+    beyond the 16-byte piece the kernel is allowed to read."""
+    n, d = a.shape
+    ld = (d + pad_to - 1) // pad_to * pad_to
+    full = torch.zeros(n, ld, device=cuda)
+    if poison and ld > (d + 3) // 4 * 4:
+        full[:, (d + 3) // 4 * 4:] = float("nan")
+    full[:, :d] = t(a, cuda)
+    return full[:, :d]
+
+
 GRAPHS = dict(GRAPHS, wide=dict(n=300, avg_deg=30.0, seed=8, hubs=4, hub_deg=290),
               single=dict(n=64, avg_deg=1.0, seed=9))
+
+
+def make_path(indptr, indices, ratio, layers, part_size, back_size, seed):
+    rng = np.random.Generator(np.random.PCG64(seed))
+    train = rng.random(len(indptr) - 1) < ratio
+    path, _ = O.prepare_execution_path(indptr, indices, train, layers, part_size, [back_size] * layers)
+    return path
+
+
 
 
 def forward_case(cuda, indptr, indices, dim, pad_to=4, seed=0, out=None):
@@ -23,7 +53,7 @@ def forward_case(cuda, indptr, indices, dim, pad_to=4, seed=0, out=None):
     feat = rng.standard_normal((n, dim)).astype(np.float32)
     deg = degrees_of(indptr)
     col = t(indices, cuda) if len(indices) else torch.zeros(0, dtype=torch.int32, device=cuda)
-    plan = capi.TilePlan.from_csr(t(indptr, cuda), col, dim)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), col)
     src = padded_rows(feat * deg[:, None], cuda, pad_to)
     got = capi.spmm_tiles(src, plan, t(deg, cuda), out=out)
     torch.cuda.synchronize()
@@ -42,7 +72,7 @@ def test_forward_dims(cuda, graph, dim):
 def test_plan_counts(cuda):
     indptr, indices = random_csr(**GRAPHS["hubs"])
     n = len(indptr) - 1
-    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda), 16)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda))
     info, deg = plan.info, np.diff(indptr)
     assert info["edges"] == len(indices) and info["rows"] == n
     assert info["nonempty_rows"] == int((deg > 0).sum()) and info["atomic_rows"] == int((deg > 64).sum())
@@ -50,30 +80,33 @@ def test_plan_counts(cuda):
     width = np.where(deg >= 5, (deg + 7) // 8 * 8, np.where(deg >= 3, 4, deg))
     pieces = np.where(deg > 64, (deg // 64) * 64 + np.where(deg % 64 >= 5, (deg % 64 + 7) // 8 * 8,
                                                              np.where(deg % 64 >= 3, 4, deg % 64)), width)
-    assert info["slots"] >= int(pieces.sum()) and info["slots"] % 8 == 0
+    assert info["slots"] >= int(pieces.sum()) and info["slots"] % 8 == 0 and info["pieces"] % 480 == 0
 
 
 def test_empty_graph_and_overwrite(cuda):
     n, dim = 50, 16
     indptr = np.zeros(n + 1, dtype=np.int32)
     out = torch.full((n, dim), 7.0, device=cuda)
-    plan = capi.TilePlan.from_csr(t(indptr, cuda), torch.zeros(0, dtype=torch.int32, device=cuda), dim)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), torch.zeros(0, dtype=torch.int32, device=cuda))
     capi.spmm_tiles(torch.ones(n, dim, device=cuda), plan, torch.ones(n, device=cuda), out=out)
     assert torch.count_nonzero(out).item() == 0, "rows without edges must come back zero"
 
 
-def test_plan_of_another_width_class_is_refused(cuda):
-    indptr, indices = random_csr(**GRAPHS["dense"])
+def test_one_plan_serves_every_row_width(cuda):
+    indptr, indices = random_csr(**GRAPHS["hubs"])
     n = len(indptr) - 1
-    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda), 16)
-    with pytest.raises(capi.EppError):
-        capi.spmm_tiles(torch.zeros(n, 64, device=cuda), plan)
+    deg = degrees_of(indptr)
+    plan = capi.TilePlan.from_csr(t(indptr, cuda), t(indices, cuda))
+    for dim in (3, 16, 22, 40, 64, 100, 128, 140):
+        feat = np.random.Generator(np.random.PCG64(dim)).standard_normal((n, dim)).astype(np.float32)
+        got = capi.spmm_tiles(padded_rows(feat * deg[:, None], cuda, 4), plan, t(deg, cuda))
+        assert_close(got.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), 2e-5, 2e-6, what=f"dim {dim}")
 
 
 def test_rows_that_are_not_consecutive_are_refused(cuda):
     ids = torch.tensor([0, 0, 1, 0], dtype=torch.int32, device=cuda)
     with pytest.raises(capi.EppError) as e:
-        capi.TilePlan.from_ids(ids, ids.clone(), 4, 2, 16)
+        capi.TilePlan.from_ids(ids, ids.clone(), 4, 2)
     assert e.value.status == capi.EPP_ERR_BAD_ARG
 
 
@@ -109,7 +142,7 @@ def test_backward_over_the_compacted_path(cuda, dim, ratio):
     d_out = rng.standard_normal((n, dim)).astype(np.float32)
     src = padded_rows(d_out * deg[:, None], cuda, 8)
     for conv in make_path(indptr, indices, ratio, 2, 6, 8, seed=dim + 1):
-        plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n, dim)
+        plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n)
         out = torch.full((n, dim), 5.0, device=cuda)
         capi.spmm_tiles(src, plan, t(deg, cuda), out=out)
         want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, d_out,
@@ -133,7 +166,7 @@ def test_agrees_with_the_group_kernel_on_rmat(cuda, dim):
     src = torch.randn(n, ld, device=cuda, generator=gen)[:, :dim]
     row, col, d = t(g.indptr, cuda), t(g.indices, cuda), t(deg, cuda)
     a = capi.spmm_forward(src, row, col, d, t(pp, cuda), t(p2n, cuda), e // n, prescaled=True)
-    b = capi.spmm_tiles(src, capi.TilePlan.from_csr(row, col, dim), d)
+    b = capi.spmm_tiles(src, capi.TilePlan.from_csr(row, col), d)
     scale = a.abs().max().item()
     assert torch.allclose(a, b, rtol=2e-5, atol=2e-6 * scale)
 
@@ -147,7 +180,7 @@ def test_pack_scaled_rows_writes_the_rows_the_path_names(cuda, dim, view):
     n = len(indptr) - 1
     deg = degrees_of(indptr)
     conv = make_path(indptr, indices, 0.1, 2, 6, 8, seed=dim)[1]
-    plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n, dim)
+    plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n)
     rng = np.random.Generator(np.random.PCG64(dim))
     x = rng.standard_normal((n, dim + 3)).astype(np.float32)
     xd = t(x, cuda)
@@ -168,3 +201,32 @@ def test_pack_scaled_rows_writes_the_rows_the_path_names(cuda, dim, view):
     assert_close(out.cpu().numpy(), want_agg, 2e-5, 2e-6, what=f"backward over packed rows dim {dim}")
     all_rows = capi.pack_scaled_rows(xv, t(deg, cuda))
     np.testing.assert_array_equal(all_rows.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("dim", [1, 3, 5, 7, 21])
+def test_group_kernel_writes_the_last_column_of_an_odd_row_into_an_aligned_view(cuda, dim):
+    """Odd row width, source rows padded to 16 bytes, and a result view whose
+    stride and base allow 8- or 16-byte stores: the last column has no partner
+    in a two-float store and must still be written, forward and backward."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(dim))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    pp, p2n = O.build_part(6, indptr)
+    src = padded_rows(feat, cuda, 4, poison=False)
+    for stride in ((dim + 1) // 2 * 2, (dim + 3) // 4 * 4 + 4):
+        wide = torch.full((n, stride), 7.0, device=cuda)
+        capi.spmm_forward(src, t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda), t(p2n, cuda), 6,
+                          out=wide[:, :dim])
+        assert_close(wide[:, :dim].cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat),
+                     what=f"forward dim {dim} stride {stride}")
+        conv = make_path(indptr, indices, 0.2, 1, 6, 8, seed=dim)[0]
+        wide.fill_(7.0)
+        capi.spmm_backward_compacted(src, t(conv["id"], cuda), t(conv["partPointer"], cuda),
+                                     t(conv["edgeList"], cuda), t(deg, cuda), conv["numParts"], 8,
+                                     out=wide[:, :dim])
+        want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, feat,
+                                         conv["numParts"])
+        assert_close(wide[:, :dim].cpu().numpy(), want, what=f"backward dim {dim} stride {stride}")
+        assert (wide[:, dim:].cpu().numpy() == 7.0).all()

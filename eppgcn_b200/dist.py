@@ -657,8 +657,23 @@ class DistHotPath:
     def gather(self, full, local):
         return all_gather_rows(full, local, self.bounds, self.group)
 
+    def _tile_plan(self, which: str, num_sources: int):
+        """The tiled-kernel plan of this rank's forward edge list, made at first use: ``"full"`` over
+        the global column ids, ``"halo"`` over positions in the exchange buffer."""
+        plans = self.__dict__.setdefault("_fwd_tile_plans", {})
+        if which not in plans:
+            col = self.col if which == "full" else self.col_c
+            plans[which] = self.capi.TilePlan.from_csr(self.row, col, num_sources=num_sources)
+        return plans[which]
+
+    @staticmethod
+    def _tiles_can_read(buf) -> bool:
+        return buf.stride(0) % 4 == 0 and buf.data_ptr() % 16 == 0
+
     def forward(self, feat_full, out_local):
         """Local forward aggregation over a whole-graph source matrix (pre-scaled rows)."""
+        if self._tiles_can_read(feat_full):
+            return self.capi.spmm_tiles(feat_full, self._tile_plan("full", self.n), self.deg_row, out=out_local)
         return self.capi.spmm_forward(feat_full, self.row, self.col, self.deg, self.pp, self.p2n, self.part_size,
                                       out=out_local, deg_row=self.deg_row, prescaled=True)
 
@@ -670,6 +685,9 @@ class DistHotPath:
 
     def _halo_spmm(self, kind, i, buf, out):
         if kind == "fwd":
+            if self._tiles_can_read(buf):
+                return self.capi.spmm_tiles(buf, self._tile_plan("halo", self.fwd_plan.num_rows), self.deg_row,
+                                            out=out)
             return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
                                           out=out, deg_row=self.deg_row, prescaled=True)
         p = self.path[i]
@@ -708,8 +726,7 @@ class DistHotPath:
         if isinstance(self.fwd_plan, DealtHalo):
             return self._dealt_op("fwd", 0, local, out_local)
         buf = self.fwd_plan.exchange(local)
-        return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
-                                      out=out_local, deg_row=self.deg_row, prescaled=True)
+        return self._halo_spmm("fwd", 0, buf, out_local)
 
     def backward_halo(self, i, d_out_local, out_local):
         p = self.path[i]

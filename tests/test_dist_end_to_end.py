@@ -17,7 +17,7 @@ from tests.test_dist import free_port
 
 
 def _install_oracle_double():
-    """Replaces the five device entry points ``DistHotPath`` calls with numpy
+    """Replaces the device entry points ``DistHotPath`` calls with numpy
     restatements that take and return CPU tensors."""
     from eppgcn_b200 import capi
     from oracle import epp_oracle as O
@@ -68,8 +68,24 @@ def _install_oracle_double():
         out.copy_(torch.from_numpy(acc.astype(np.float32)))
         return out
 
+    class TilePlan:
+        """Double of the tiled kernel's plan: just remembers the edge list."""
+
+        def __init__(self, row_ptr, col_idx):
+            self.row_ptr, self.col_idx = row_ptr, col_idx
+
+        @classmethod
+        def from_csr(cls, row_ptr, col_idx, num_sources=None):
+            assert num_sources is None or int(col_idx.max()) < num_sources
+            return cls(row_ptr, col_idx)
+
+    def spmm_tiles(src, plan, row_scale=None, out=None):
+        return spmm_forward(src, plan.row_ptr, plan.col_idx, row_scale, None, None, out=out, deg_row=row_scale,
+                            prescaled=True)
+
     for name, fn in dict(mask_forward=mask_forward, compact_mask=compact_mask, split_parts=split_parts,
-                         spmm_forward=spmm_forward, spmm_backward_compacted=spmm_backward_compacted).items():
+                         spmm_forward=spmm_forward, spmm_backward_compacted=spmm_backward_compacted,
+                         spmm_tiles=spmm_tiles, TilePlan=TilePlan).items():
         setattr(capi, name, fn)
 
 

@@ -10,12 +10,58 @@ import json
 import os
 import time
 
+import numpy as np
 import torch
 import torch.distributed as dist
 
 import bench as B
 from eppgcn_b200 import graphs
 from eppgcn_b200.dist import DistHotPath, DealtHalo  # noqa: F401  (DealtHalo: plan type of the default mode)
+
+
+def check_shard(hp, ops, staged, local_in, outs, one, dev, rank, world, rows_wanted=50_000):
+    """Runs every aggregation of the epoch once more and compares this rank's result rows (a sample
+    that includes its 500 rows of highest degree) with the float64 oracle over the rank's shard of
+    the relabelled graph and the inputs of all ranks.  Forward inputs are pre-scaled rows
+    (out = deg[r] * sum x[c]); backward inputs are raw (out = deg[r] * sum deg[c] * x[c]).
+    Tolerance |got - want| <= 2e-6 + 2e-5 |want|.  Returns the `check` object (the worst rank's)."""
+    from oracle import epp_oracle as O
+    sh = hp.shard
+    ip = np.asarray(sh.indptr, dtype=np.int64)
+    ix = np.asarray(sh.indices)
+    deg = hp.deg.cpu().numpy().astype(np.float64)
+    deg_row = deg[sh.v0:sh.v1]
+    n_loc = hp.n_loc
+    lens = np.diff(ip)
+    top = np.argsort(-lens, kind="stable")[:min(500, n_loc)]
+    rng = np.random.Generator(np.random.PCG64(11 + rank))
+    rows = np.unique(np.concatenate([top, rng.choice(n_loc, size=min(rows_wanted, n_loc), replace=False)]))
+    worst, detail = -np.inf, {}
+    for k, (kind, i, d) in enumerate(ops):
+        mine = torch.cat([v for v in staged[k]], dim=1).contiguous() if local_in[k] is None else local_in[k].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        x = torch.cat(parts, dim=0).cpu().numpy().astype(np.float64)           # rows in the partition's numbering
+        one(k)
+        torch.cuda.synchronize()
+        got = outs[k].cpu().numpy()[rows]
+        if kind == "fwd":
+            want = O.spmm_rows(ip, ix, rows, x, row_scale=deg_row)
+        else:
+            p = hp.path[i]
+            v = p["valid"]
+            want = O.spmm_rows_from_pairs(p["id"][:v].cpu().numpy(), p["edges"][:v].cpu().numpy(), n_loc, rows,
+                                          x * deg[:x.shape[0], None], row_scale=deg_row)
+        excess = float((np.abs(got - want) - (2e-6 + 2e-5 * np.abs(want))).max())
+        detail[f"{kind}_l{i + 1}"] = excess
+        worst = max(worst, excess)
+    t = torch.tensor([worst], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if hp.fabric is not None:
+        hp.fabric.check()
+    return {"rows_per_rank": int(rows.size), "max_excess": float(t.item()), "ok": bool(t.item() <= 0),
+            "tolerance": "|got-want| <= 2e-6 + 2e-5|want| against float64 on every rank's sampled rows",
+            "rank0_per_aggregation": detail}
 
 
 def run_bench(args, rank: int, world: int, dev):
@@ -148,6 +194,13 @@ def run_bench(args, rank: int, world: int, dev):
     if hp.fabric is not None:
         hp.fabric.check()
 
+    # parity of what was timed, outside the timed region: every aggregation's local result on sampled
+    # rows against the float64 oracle of this rank's shard (host-drawn workloads; the device-drawn graph
+    # is too large for a host oracle)
+    check = None
+    if not device_drawn and mode in ("balanced", "balanced_halo") and not getattr(args, "no_check", False):
+        check = check_shard(hp, ops, staged, local_in, outs, one, dev, rank, world)
+
     # e2e: host buffers, every step stages this rank's rows in and its results out
     host_in = [[torch.empty(x.shape, pin_memory=True).copy_(x) for x in views] for views in staged]
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
@@ -237,7 +290,7 @@ def run_bench(args, rank: int, world: int, dev):
                          "frac": round(achieved / peak, 4), "traffic": None, "algorithmic_bytes": int(algo),
                          "note": "one GPU's compulsory bytes over its local kernel time; the per-kernel roofline "
                                  "with ncu traffic is reported by the 1-GPU run of the default workload"},
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(), "check": check,
             "e2e": {"value": round(e2e.item(), 4), "unit": "ms/epoch", "h2d_bytes_per_step": int(byts[0]),
                     "d2h_bytes_per_step": int(byts[1]),
                     "what": "each rank stages its rows from pinned host memory, exchanges, aggregates, copies results back"},

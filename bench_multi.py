@@ -19,6 +19,39 @@ from eppgcn_b200 import graphs
 from eppgcn_b200.dist import DistHotPath, DealtHalo  # noqa: F401  (DealtHalo: plan type of the default mode)
 
 
+def count_launches(hp, step):
+    """Runs one step with the C-ABI wrappers of ``hp.capi`` counting the kernels they enqueue: one per
+    call, plus the row-clearing kernel of a tiled aggregation whose plan lists rows to clear (a plan
+    that clears the whole result uses a memset, which is not a kernel), plus the clearing kernel of a
+    group-kernel call that writes a column block."""
+    capi = hp.capi
+    names = ["push_rows", "peer_barrier", "spmm_tiles", "pack_scaled_rows", "spmm_forward", "spmm_backward_compacted"]
+    saved = {n: getattr(capi, n) for n in names}
+    count = [0]
+
+    def wrap(name, fn):
+        def counted(*a, **k):
+            count[0] += 1
+            if name == "spmm_tiles":
+                info = a[1].info
+                count[0] += 1 if info["cleared_rows"] and not info["clears_whole_result"] else 0
+            elif name in ("spmm_forward", "spmm_backward_compacted"):
+                out = k.get("out")
+                count[0] += 1 if out is not None and out.dim() == 2 and out.stride(0) != out.size(1) else 0
+            return fn(*a, **k)
+        return counted
+
+    for n in names:
+        setattr(capi, n, wrap(n, saved[n]))
+    try:
+        step()
+        torch.cuda.synchronize()
+    finally:
+        for n in names:
+            setattr(capi, n, saved[n])
+    return count[0]
+
+
 def check_shard(hp, ops, staged, local_in, outs, one, dev, rank, world, rows_wanted=50_000):
     """Runs every aggregation of the epoch once more and compares this rank's result rows (a sample
     that includes its 500 rows of highest degree) with the float64 oracle over the rank's shard of
@@ -109,9 +142,11 @@ def run_bench(args, rank: int, world: int, dev):
     ops = [("fwd", i, dims[i]) for i in range(L)] + [("bwd", i, dims[i]) for i in reversed(range(L))]
     # forward inputs as the update step leaves them (padded rows), backward inputs as autograd does (dense)
     if dealt:
-        # the producer of an input writes this rank's rows straight into the exchange buffers
-        local_in = [None] * len(ops)
-        staged = [hp.halo_inputs(kind, i, d) for kind, i, d in ops]
+        # forward: the producer (the update step) writes this rank's pre-scaled rows straight into the
+        # exchange buffers; backward: the rows come from autograd, unscaled, in a matrix of their own, and
+        # are multiplied by deg while they are copied into place
+        local_in = [None if kind == "fwd" else torch.randn(n_loc, d, device=dev, generator=gen) for kind, _, d in ops]
+        staged = [hp.halo_inputs(kind, i, d) if kind == "fwd" else [local_in[k]] for k, (kind, i, d) in enumerate(ops)]
         for views in staged:
             for v in views:
                 v.normal_(generator=gen)
@@ -135,7 +170,7 @@ def run_bench(args, rank: int, world: int, dev):
 
     def one(k):
         kind, i, d = ops[k]
-        if kind == "bwd" and compact_bwd:
+        if kind == "bwd" and (compact_bwd or halo):
             hp.backward_halo(i, local_in[k], outs[k])
         elif halo:
             hp.forward_halo(local_in[k], outs[k])
@@ -161,6 +196,9 @@ def run_bench(args, rank: int, world: int, dev):
     def step():
         for k in range(len(ops)):
             one(k)
+
+    # this library's kernels per epoch, counted on one untimed step by wrapping the C-ABI calls
+    launches_per_step = count_launches(hp, step)
 
     stream = torch.cuda.current_stream()
     with B.ClockSampler(dev.index) as clocks:
@@ -247,14 +285,7 @@ def run_bench(args, rank: int, world: int, dev):
                 algo += (4 * p["valid"] + 4 * (p["parts"] + 1) + 4 * p["parts"] + 4 * d * src_rows
                          + 4 * (p["rows"] + src_rows) + 4 * d * n_loc)
         achieved = algo / (kms.item() * 1e-3) / 1e9
-        # this library's kernels per epoch: one SpMM per aggregation and column chunk (plus the zeroing kernel of a
-        # column block), and with the push transport one push per chunk and two barriers per aggregation
-        launches = 0
-        for kind, i, d in ops:
-            c = len((hp.fwd_plan if kind == "fwd" else hp.path[i]["plan"]).buffers(d, hp.chunks)) if dealt else 1
-            launches += c * (2 if c > 1 else 1)
-            if dealt and hp.fabric is not None:
-                launches += c + 2
+        launches = launches_per_step
         line = {
             "metric": f"{L}-layer GCN ms/epoch (fwd+bwd aggregation)", "value": round(ms.item(), 4),
             "unit": "ms/epoch", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),

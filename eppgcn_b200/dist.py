@@ -365,7 +365,7 @@ class DealtHalo:
             dist.all_to_all_single(self.send_idx, request, self.send_counts, self.recv_counts, group=group)
         self.num_remote, self.num_rows = r, r + n_loc
         self.order = torch.cat([self.needed, torch.arange(v0, v0 + n_loc, device=dev)])
-        self._bufs = {}
+        self._bufs, self._stamps = {}, {}
         if self.fabric is not None:
             # peer stores: where this rank's rows start in every reader's buffer, and one buffer size for all ranks
             first_in = cut[:-1].clone()
@@ -408,21 +408,39 @@ class DealtHalo:
         there (column block by column block) saves the copy :meth:`start` makes."""
         return [buf[self.num_remote:] for _, buf in self.buffers(d, chunks)]
 
-    def start(self, local, chunks: int = 1, d: int = 0):
+    def _place_own(self, buf, rows, scale):
+        """This rank's rows into their place in a source buffer; with ``scale`` (its own
+        vertices' source-side factors) they are multiplied on the way, so that every
+        rank's edges find pre-scaled rows."""
+        if scale is None:
+            buf[self.num_remote:].copy_(rows)
+        else:
+            from eppgcn_b200 import capi
+            capi.pack_scaled_rows(rows, scale, None, out=buf[self.num_remote:])
+
+    def start(self, local, chunks: int = 1, d: int = 0, scale=None):
         """Enqueues the exchange of ``local [n_loc, d]``, one all-to-all per column
         chunk; ``local = None``: the rows already sit in :meth:`own_rows` (``d``
-        names the width).  Returns ``[(work, buffer)]``; ``work.wait()`` makes the
-        current stream wait for that chunk only."""
+        names the width).  ``scale [n_loc]``: the rows are multiplied by it while they
+        are copied into place (not with ``local = None``).  Returns ``[(work, buffer)]``;
+        ``work.wait()`` makes the current stream wait for that chunk only."""
         d = local.size(1) if local is not None else d
         out = []
         bufs = self.buffers(d, chunks)
         if self.fabric is not None and isinstance(bufs[0][0], list):
-            # peer stores: wait until no rank reads these buffers any more, push, wait until every push has landed
-            self.fabric.barrier()
+            # Peer stores: wait until no rank reads these buffers any more, push, wait until every push has
+            # landed.  The first wait is only needed when no barrier has passed since these buffers were last
+            # aggregated from: a rank arrives at any later barrier after that aggregation (same stream), so
+            # whoever has left such a barrier may overwrite them.  An epoch that alternates between buffers
+            # (layers of different width, forward and backward) therefore pays one barrier per aggregation.
+            key = (d, len(bufs))
+            stamp = self._stamps.get(key)
+            if stamp is None or self.fabric.count <= stamp or (self.overlap and len(bufs) > 1):
+                self.fabric.barrier()
             if local is not None:
                 for c, (_, buf) in enumerate(bufs):
                     dc = buf.size(1)
-                    buf[self.num_remote:].copy_(local[:, c * dc:(c + 1) * dc])
+                    self._place_own(buf, local[:, c * dc:(c + 1) * dc], scale)
 
             def push(peers, buf):
                 wide = _padded_rows(buf[self.num_remote:])
@@ -434,6 +452,7 @@ class DealtHalo:
                     push(peers, buf)
                     out.append((None, buf))
                 self.fabric.barrier()
+                self._stamps[key] = self.fabric.count
                 return out
             # chunk 0 on this stream; the later chunks on a side stream, each behind the one before it, so that
             # they travel while the caller aggregates the chunks that have landed
@@ -455,7 +474,7 @@ class DealtHalo:
         for c, (send, buf) in enumerate(bufs):
             dc = send.size(1)
             if local is not None:
-                buf[self.num_remote:].copy_(local[:, c * dc:(c + 1) * dc])
+                self._place_own(buf, local[:, c * dc:(c + 1) * dc], scale)
             part = buf[self.num_remote:]
             work = None
             if self.world > 1:                   # every rank joins, also one that neither sends nor receives
@@ -691,15 +710,37 @@ class DistHotPath:
             return self.capi.spmm_forward(buf, self.row, self.col_c, self.deg, self.pp, self.p2n, self.part_size,
                                           out=out, deg_row=self.deg_row, prescaled=True)
         p = self.path[i]
+        if p.get("prescaled", {}).get(buf.size(1)):
+            # the exchange already multiplied every row by its source-side factor (see _dealt_op)
+            if "tile_plan" not in p:
+                p["tile_plan"] = self.capi.TilePlan.from_ids(p["id"], p["edges_c"], p["valid"], self.shard.num_rows,
+                                                             num_sources=p["plan"].num_rows)
+            return self.capi.spmm_tiles(buf, p["tile_plan"], self.deg_row, out=out)
         return self.capi.spmm_backward_compacted(buf, p["id"], p["pp"], p["edges_c"], p["deg_c"], p["parts"],
                                                  self.back_size, out=out, deg_row=self.deg_row,
                                                  num_rows=self.shard.num_rows)
 
     def _dealt_op(self, kind, i, local, out_local):
         """Chunked exchange + aggregation: chunk ``c`` is aggregated (straight into
-        its column block of ``out_local``) while chunk ``c + 1`` travels."""
+        its column block of ``out_local``) while chunk ``c + 1`` travels.  A backward
+        layer's rows are multiplied by their source-side factor while they are copied
+        into the exchange buffer (every rank scales the rows it owns), so that the
+        aggregation runs the tile kernel on pre-scaled rows; that needs the caller's
+        rows (``local``) and 16-byte aligned buffer rows, else the group kernel
+        applies the factor per edge."""
         plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
-        pending = plan.start(local, self.chunks, out_local.size(1))
+        scale = None
+        if kind == "bwd":
+            d = out_local.size(1)
+            bufs = plan.buffers(d, self.chunks)
+            aligned = all(self._tiles_can_read(b) for _, b in bufs)
+            p = self.path[i]
+            want = local is not None and aligned
+            # remembered per buffer width: the kernels-only timing path re-runs the aggregation on the buffers
+            # as the last exchange left them
+            p.setdefault("prescaled", {})[bufs[0][1].size(1)] = want
+            scale = self.deg_row if want else None
+        pending = plan.start(local, self.chunks, out_local.size(1), scale=scale)
         dc = out_local.size(1) // len(pending)
         for c, (work, buf) in enumerate(pending):
             if work is not None:
@@ -712,6 +753,15 @@ class DistHotPath:
         :meth:`DealtHalo.own_rows`); pass ``None`` as the input afterwards."""
         plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
         return plan.own_rows(d, self.chunks)
+
+    def check(self):
+        """Raises if a bounded wait of the peer-store transport ran out.  After such a
+        time-out later barriers no longer wait and the exchange buffers may be half
+        filled, so results must not be trusted: call this at a point where a host
+        synchronisation is affordable (once per epoch, or before results leave the
+        rank).  A no-op for the NCCL transports, whose errors surface as exceptions."""
+        if self.fabric is not None:
+            self.fabric.check()
 
     def halo_local(self, kind, i, out_local):
         """Only the aggregation kernels of one operation, on the buffers the last exchange filled."""

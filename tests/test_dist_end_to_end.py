@@ -69,23 +69,38 @@ def _install_oracle_double():
         return out
 
     class TilePlan:
-        """Double of the tiled kernel's plan: just remembers the edge list."""
+        """Double of the tiled kernel's plan: just remembers the edge list as (row, source) pairs."""
 
-        def __init__(self, row_ptr, col_idx):
-            self.row_ptr, self.col_idx = row_ptr, col_idx
+        def __init__(self, rows, cols, num_rows):
+            self.rows, self.cols, self.num_rows = rows, cols, num_rows
 
         @classmethod
         def from_csr(cls, row_ptr, col_idx, num_sources=None):
-            assert num_sources is None or int(col_idx.max()) < num_sources
-            return cls(row_ptr, col_idx)
+            assert num_sources is None or col_idx.numel() == 0 or int(col_idx.max()) < num_sources
+            ptr = row_ptr.numpy().astype(np.int64)
+            return cls(np.repeat(np.arange(len(ptr) - 1), np.diff(ptr)), col_idx.numpy().astype(np.int64), len(ptr) - 1)
+
+        @classmethod
+        def from_ids(cls, ids, col_idx, num_edges, num_rows, num_sources=None):
+            assert num_sources is None or num_edges == 0 or int(col_idx[:num_edges].max()) < num_sources
+            return cls(ids.numpy()[:num_edges].astype(np.int64), col_idx.numpy()[:num_edges].astype(np.int64), num_rows)
 
     def spmm_tiles(src, plan, row_scale=None, out=None):
-        return spmm_forward(src, plan.row_ptr, plan.col_idx, row_scale, None, None, out=out, deg_row=row_scale,
-                            prescaled=True)
+        acc = np.zeros((plan.num_rows, src.size(1)))
+        np.add.at(acc, plan.rows, src.numpy().astype(np.float64)[plan.cols])
+        if row_scale is not None:
+            acc *= row_scale.numpy().astype(np.float64)[:plan.num_rows, None]
+        out.copy_(torch.from_numpy(acc.astype(np.float32)))
+        return out
+
+    def pack_scaled_rows(x, scale, plan=None, out=None, pad_to=8):
+        assert plan is None
+        out.copy_(x * scale[:, None])
+        return out
 
     for name, fn in dict(mask_forward=mask_forward, compact_mask=compact_mask, split_parts=split_parts,
                          spmm_forward=spmm_forward, spmm_backward_compacted=spmm_backward_compacted,
-                         spmm_tiles=spmm_tiles, TilePlan=TilePlan).items():
+                         spmm_tiles=spmm_tiles, TilePlan=TilePlan, pack_scaled_rows=pack_scaled_rows).items():
         setattr(capi, name, fn)
 
 

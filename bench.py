@@ -720,6 +720,9 @@ def main():
                         "chunk c is aggregated")
     p.add_argument("--transport", default="push", choices=["push", "nccl"],
                    help="balanced_halo: peer stores by this library's kernel, or NCCL all-to-all")
+    p.add_argument("--lead-barrier", action="store_true",
+                   help="balanced_halo, push transport: always wait for the readers of a buffer before pushing into "
+                        "it (default: only when no other barrier has passed since it was read)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-full-epoch", action="store_true")
     p.add_argument("--no-check", action="store_true")

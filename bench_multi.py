@@ -132,6 +132,9 @@ def run_bench(args, rank: int, world: int, dev):
     hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=chunks,
                      transport=getattr(args, "transport", "push"), overlap=getattr(args, "overlap", False))
     dealt = mode == "balanced_halo"
+    if dealt and getattr(args, "lead_barrier", False):
+        for plan in [hp.fwd_plan] + [p["plan"] for p in hp.path]:
+            plan.lead_barrier = True
     if device_drawn:
         ds.indptr = ds.indices = None           # the shard is all this rank needs from here on
         torch.cuda.empty_cache()

@@ -34,12 +34,16 @@ SIGNATURES = {
     "eppgcn_spmm_tiles": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
+    "eppgcn_weight_grad_rows": (_I, [_P, _P, _LL, _P, _LL, _P, _I, _I, _I, _P]),
+    "eppgcn_tile_plan_active_rows": (_I, [_P, _P, _P]),
     "eppgcn_mask_forward": (_I, [_P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _P]),
     "eppgcn_compact_scratch_bytes": (_SZ, [_I]),
     "eppgcn_compact_mask": (_I, [_P, _P, _P, _P, _I, _P, _SZ, _P, _P, _I, _P]),
     "eppgcn_compact_mask_static": (_I, [_P, _P, _P, _P, _I, _P, _P, _P]),
     "eppgcn_split_scratch_bytes": (_SZ, [_I]),
     "eppgcn_split_parts": (_I, [_P, _I, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
+    "eppgcn_build_part_scratch_bytes": (_SZ, [_I]),
+    "eppgcn_build_part": (_I, [_P, _I, _I, _P, _I, _P, _I, _P, _SZ, _P, _P, _I, _P]),
     "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
     "eppgcn_push_rows": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _LL, _P]),
     "eppgcn_peer_barrier": (_I, [_P, _I, _I, C.c_uint, _LL, _P, _P]),
@@ -128,12 +132,19 @@ def update_scaled(x, w, scale=None, pad_to=8):
     return full[:, :dout]
 
 
-def weight_grad(x, d):
-    """``x.T @ d`` for a tall ``x [N, k]`` and ``d [N, dout]``."""
+def weight_grad(x, d, plan=None):
+    """``x.T @ d`` for a tall ``x [N, k]`` and ``d [N, dout]``; with a tile ``plan`` only over the
+    rows that have edges in it (the other rows of ``d`` are zero by construction)."""
     k, dout = x.size(1), d.size(1)
     dw = torch.empty(k, dout, device=x.device, dtype=torch.float32)
-    check(lib().eppgcn_weight_grad(dw.data_ptr(), x.data_ptr(), _row_stride(x, "x"), d.data_ptr(),
-                                   _row_stride(d, "d"), x.size(0), k, dout, _stream()))
+    if plan is None:
+        check(lib().eppgcn_weight_grad(dw.data_ptr(), x.data_ptr(), _row_stride(x, "x"), d.data_ptr(),
+                                       _row_stride(d, "d"), x.size(0), k, dout, _stream()))
+        return dw
+    rows, count = _P(), _I()
+    check(lib().eppgcn_tile_plan_active_rows(plan._handle, C.byref(rows), C.byref(count)))
+    check(lib().eppgcn_weight_grad_rows(dw.data_ptr(), x.data_ptr(), _row_stride(x, "x"), d.data_ptr(),
+                                        _row_stride(d, "d"), rows, count.value, k, dout, _stream()))
     return dw
 
 
@@ -315,6 +326,27 @@ def split_parts(node_deg, num_edges, part_size, mode=0, out_len=None):
         scratch.data_ptr(), nbytes, counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
     parts, _ = _finish(counter)
     return out, parts
+
+
+def build_part_device(part_size: int, row_ptr: torch.Tensor, num_edges: int | None = None, mode=0):
+    """Neighbour groups of a CSR whose row pointer lives on the device: returns
+    ``(part_ptr[P+1], part2node[P])`` as int32 CUDA tensors, equal to what
+    :func:`build_part` returns for the same row pointer on the host."""
+    n = row_ptr.numel() - 1
+    dev = row_ptr.device
+    if num_edges is None:
+        num_edges = int(row_ptr[-1].item())
+    cap = num_edges // max(int(part_size), 1) + n + 1
+    part_ptr = torch.empty(cap + 1, dtype=torch.int32, device=dev)
+    part2node = torch.empty(cap, dtype=torch.int32, device=dev)
+    nbytes = lib().eppgcn_build_part_scratch_bytes(n)
+    scratch = torch.empty((nbytes + 7) // 8, dtype=torch.int64, device=dev)
+    counter = torch.empty(2, dtype=torch.int32, device=dev)
+    check(lib().eppgcn_build_part(_dev(row_ptr, torch.int32, "row_ptr"), n, int(part_size), part_ptr.data_ptr(),
+                                  cap + 1, part2node.data_ptr(), cap, scratch.data_ptr(), nbytes,
+                                  counter.data_ptr(), counter.data_ptr() + 4, mode, _stream()))
+    parts, _ = _finish(counter)
+    return part_ptr[:parts + 1].clone(), part2node[:parts].clone()
 
 
 def push_rows(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, dim=None, start_row=0):

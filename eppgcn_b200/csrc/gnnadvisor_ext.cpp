@@ -197,11 +197,17 @@ torch::Tensor update_scaled_padded(const torch::Tensor &x, const torch::Tensor &
   auto full = at::empty({n, ld}, x.options());
   auto view = full.narrow(1, 0, d);
   const bool aligned = x.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(x.data_ptr<float>()) % 16 == 0;
-  if (d <= 32 && aligned && n > 0) {
-    epp_check(eppgcn_update_scaled(full.data_ptr<float>(), ld, x.data_ptr<float>(), x.stride(0), w.data_ptr<float>(),
-                                   d, degrees.data_ptr<float>(), static_cast<int>(n), static_cast<int>(k),
-                                   static_cast<int>(d), static_cast<int>(ld - d), current_stream()),
-              "eppgcn_update_scaled");
+  if (aligned && n > 0 && n < (1LL << 31)) {
+    // 32 output columns per launch; the last block also clears the padding columns
+    for (int64_t c0 = 0; c0 < d; c0 += 32) {
+      const int cols = static_cast<int>(std::min<int64_t>(32, d - c0));
+      const bool last = c0 + cols == d;
+      epp_check(eppgcn_update_scaled(full.data_ptr<float>() + c0, ld, x.data_ptr<float>(), x.stride(0),
+                                     w.data_ptr<float>() + c0, d, degrees.data_ptr<float>(), static_cast<int>(n),
+                                     static_cast<int>(k), cols, last ? static_cast<int>(ld - d) : 0,
+                                     current_stream()),
+                "eppgcn_update_scaled");
+    }
   } else {
     at::mm_out(view, x, w);
     view.mul_(degrees.narrow(0, 0, n).unsqueeze(1));
@@ -215,26 +221,58 @@ torch::Tensor update_scaled_padded(const torch::Tensor &x, const torch::Tensor &
 // d_input once, where cuBLAS takes several times longer on these shapes.  Shapes
 // outside the kernels' limits go through torch::mm.
 std::vector<torch::Tensor> backward_update(const torch::Tensor &d_prime, const torch::Tensor &X,
-                                           const torch::Tensor &W) {
+                                           const torch::Tensor &W, const eppgcn_tile_plan *plan = nullptr,
+                                           bool need_d_input = true) {
   const int64_t n = d_prime.size(0), dout = d_prime.size(1), din = W.size(0);
-  const bool ok = n > 0 && n < (1LL << 31) && dout <= 32 && din * ((dout + 3) / 4 * 4) <= 4096 && din % 4 == 0 &&
-                  X.stride(0) % 4 == 0 && reinterpret_cast<uintptr_t>(X.data_ptr<float>()) % 16 == 0 &&
+  const bool ok = n > 0 && n < (1LL << 31) && din % 4 == 0 && dout % 4 == 0 && X.stride(0) % 4 == 0 &&
+                  reinterpret_cast<uintptr_t>(X.data_ptr<float>()) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(d_prime.data_ptr<float>()) % 16 == 0;
-  if (!ok) return {at::mm(d_prime, W.transpose(0, 1)), at::mm(X.transpose(0, 1), d_prime)};
-  auto wt = W.transpose(0, 1).contiguous();                 // [Dout, Din]
-  auto d_input = at::empty({n, din}, d_prime.options());
-  for (int64_t c0 = 0; c0 < din; c0 += 32) {                // 32 output columns per launch
-    const int cols = static_cast<int>(std::min<int64_t>(32, din - c0));
-    epp_check(eppgcn_update_scaled(d_input.data_ptr<float>() + c0, din, d_prime.data_ptr<float>(), dout,
-                                   wt.data_ptr<float>() + c0, din, nullptr, static_cast<int>(n),
-                                   static_cast<int>(dout), cols, 0, current_stream()),
-              "eppgcn_update_scaled");
+  const bool narrow_ok = n > 0 && n < (1LL << 31) && dout <= 32 && din * ((dout + 3) / 4 * 4) <= 4096 &&
+                         din % 4 == 0 && X.stride(0) % 4 == 0 &&
+                         reinterpret_cast<uintptr_t>(X.data_ptr<float>()) % 16 == 0 &&
+                         reinterpret_cast<uintptr_t>(d_prime.data_ptr<float>()) % 16 == 0;
+  if (!ok && !narrow_ok)
+    return {need_d_input ? at::mm(d_prime, W.transpose(0, 1)) : at::empty({0}, d_prime.options()),
+            at::mm(X.transpose(0, 1), d_prime)};
+  torch::Tensor d_input = at::empty({0}, d_prime.options());
+  if (need_d_input) {
+    auto wt = W.transpose(0, 1).contiguous();                 // [Dout, Din]
+    d_input = at::empty({n, din}, d_prime.options());
+    for (int64_t c0 = 0; c0 < din; c0 += 32) {                // 32 output columns per launch
+      const int cols = static_cast<int>(std::min<int64_t>(32, din - c0));
+      epp_check(eppgcn_update_scaled(d_input.data_ptr<float>() + c0, din, d_prime.data_ptr<float>(), dout,
+                                     wt.data_ptr<float>() + c0, din, nullptr, static_cast<int>(n),
+                                     static_cast<int>(dout), cols, 0, current_stream()),
+                "eppgcn_update_scaled");
+    }
   }
+  // d_weight: only the rows of the execution path face a non-zero row of d' (EPPGCN_kernel.cu:607,616
+  // sketches the same restriction); wide shapes go block by block (32 columns of d', <= 128 of X)
+  const int *rows = nullptr;
+  int listed = 0;
+  if (plan) epp_check(eppgcn_tile_plan_active_rows(plan, &rows, &listed), "eppgcn_tile_plan_active_rows");
+  const bool by_rows = plan && listed < n;
   auto d_weight = at::empty({din, dout}, d_prime.options());
-  epp_check(eppgcn_weight_grad(d_weight.data_ptr<float>(), X.data_ptr<float>(), X.stride(0),
-                               d_prime.data_ptr<float>(), dout, static_cast<int>(n), static_cast<int>(din),
-                               static_cast<int>(dout), current_stream()),
-            "eppgcn_weight_grad");
+  const int64_t cb = std::min<int64_t>(dout, 32);
+  const int64_t kb = std::max<int64_t>(4, std::min<int64_t>(din, 4096 / ((cb + 3) / 4 * 4) / 4 * 4));
+  const bool whole = cb == dout && kb == din;
+  for (int64_t c0 = 0; c0 < dout; c0 += cb) {
+    const int cols = static_cast<int>(std::min<int64_t>(cb, dout - c0));
+    for (int64_t k0 = 0; k0 < din; k0 += kb) {
+      const int ks = static_cast<int>(std::min<int64_t>(kb, din - k0));
+      auto block = whole ? d_weight : at::empty({ks, cols}, d_prime.options());
+      const float *xp = X.data_ptr<float>() + k0, *dp = d_prime.data_ptr<float>() + c0;
+      if (by_rows)
+        epp_check(eppgcn_weight_grad_rows(block.data_ptr<float>(), xp, X.stride(0), dp, dout, rows, listed, ks, cols,
+                                          current_stream()),
+                  "eppgcn_weight_grad_rows");
+      else
+        epp_check(eppgcn_weight_grad(block.data_ptr<float>(), xp, X.stride(0), dp, dout, static_cast<int>(n), ks,
+                                     cols, current_stream()),
+                  "eppgcn_weight_grad");
+      if (!whole) d_weight.narrow(0, k0, ks).narrow(1, c0, cols).copy_(block);
+    }
+  }
   return {d_input, d_weight};
 }
 
@@ -341,10 +379,10 @@ void mask_forward(torch::Tensor id, torch::Tensor partPointer, torch::Tensor edg
 // ours_backward(d_output, X, W, id, partPointer, edgeList, degrees, partSize,
 //               numParts, layer, blockx, blocky) -> [d_input, d_weight]
 // EPPGCN.cpp:157-184, EPPGCN_kernel.cu:547-624.
-std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
-                                         torch::Tensor id, torch::Tensor partPointer, torch::Tensor edgeList,
-                                         torch::Tensor degrees, int partSize, int numParts, int layer,
-                                         int blockx, int blocky) {
+std::vector<torch::Tensor> ours_backward_impl(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
+                                              torch::Tensor id, torch::Tensor partPointer, torch::Tensor edgeList,
+                                              torch::Tensor degrees, int partSize, int numParts, int layer,
+                                              int blockx, int blocky, bool need_d_input) {
   CHECK_INPUT(d_output); CHECK_INPUT(X); CHECK_INPUT(W); CHECK_INPUT(id); CHECK_INPUT(partPointer);
   CHECK_INPUT(edgeList); CHECK_INPUT(degrees);
   CHECK_F32(d_output); CHECK_F32(X); CHECK_F32(W); CHECK_F32(degrees);
@@ -354,9 +392,10 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
   c10::cuda::CUDAGuard guard(d_output.device());
   const int64_t n = d_output.size(0), d = d_output.size(1);
   torch::Tensor d_input_prime;
+  const eppgcn_tile_plan *plan = nullptr;
   if (plans_enabled() && n > 0) {
     ScopedTime t(2, layer);
-    const eppgcn_tile_plan *plan = backward_plan(id, partPointer, edgeList, numParts, n);
+    plan = backward_plan(id, partPointer, edgeList, numParts, n);
     d_input_prime = aggregate_planned(plan, pack_scaled(plan, d_output, degrees), degrees, n);
   } else {
     d_input_prime = at::empty({n, d}, d_output.options());
@@ -369,13 +408,58 @@ std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X
               "eppgcn_spmm_backward_compacted");
   }
   ScopedTime t(3);
-  return backward_update(d_input_prime, X, W);
+  return backward_update(d_input_prime, X, W, plan, need_d_input);
+}
+
+std::vector<torch::Tensor> ours_backward(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
+                                         torch::Tensor id, torch::Tensor partPointer, torch::Tensor edgeList,
+                                         torch::Tensor degrees, int partSize, int numParts, int layer,
+                                         int blockx, int blocky) {
+  return ours_backward_impl(d_output, X, W, id, partPointer, edgeList, degrees, partSize, numParts, layer, blockx,
+                            blocky, true);
+}
+
+// ours_backward for a layer whose input needs no gradient (the first layer of a model: its input is
+// the feature matrix): returns [empty, d_weight] and skips the d' @ W^T product and its [N, Din] result.
+// Not in the reference, which computes that product for every layer.
+std::vector<torch::Tensor> ours_backward_weight_only(torch::Tensor d_output, torch::Tensor X, torch::Tensor W,
+                                                     torch::Tensor id, torch::Tensor partPointer,
+                                                     torch::Tensor edgeList, torch::Tensor degrees, int partSize,
+                                                     int numParts, int layer, int blockx, int blocky) {
+  return ours_backward_impl(d_output, X, W, id, partPointer, edgeList, degrees, partSize, numParts, layer, blockx,
+                            blocky, false);
 }
 
 // build_part(partSize, indptr) -> [partPtr, part2Node]      EPPGCN.cpp:186-227
 std::vector<torch::Tensor> build_part(int partSize, torch::Tensor indptr) {
-  TORCH_CHECK(!indptr.is_cuda(), "indptr must be a CPU tensor");
   CHECK_I32(indptr);
+  if (indptr.is_cuda()) {
+    // Beyond the reference (its build_part takes a CPU tensor only): a row pointer that already
+    // lives on the device is partitioned there, and the groups come back as CUDA tensors.
+    TORCH_CHECK(indptr.dim() == 1 && indptr.numel() >= 1, "indptr must be a 1-D tensor of num_nodes + 1 entries");
+    TORCH_CHECK(partSize >= 1, "partSize must be >= 1, got ", partSize);
+    c10::cuda::CUDAGuard guard(indptr.device());
+    auto ip = indptr.contiguous();
+    const int n = static_cast<int>(ip.numel() - 1);
+    const int64_t edges = n > 0 ? ip[n].item<int>() : 0;
+    const int64_t cap = edges / partSize + n + 1;
+    TORCH_CHECK(cap + 1 < (1LL << 31), "group count exceeds int32");
+    auto partPtr = at::empty({cap + 1}, ip.options());
+    auto part2Node = at::empty({cap}, ip.options());
+    const size_t bytes = eppgcn_build_part_scratch_bytes(n);
+    auto scratch = at::empty({static_cast<int64_t>((bytes + 7) / 8)}, ip.options().dtype(at::kLong));
+    auto counter = at::empty({2}, ip.options());
+    for (int mode = 0; mode < 2; ++mode) {
+      epp_check(eppgcn_build_part(ip.data_ptr<int>(), n, partSize, partPtr.data_ptr<int>(), static_cast<int>(cap + 1),
+                                  part2Node.data_ptr<int>(), static_cast<int>(cap), scratch.data_ptr(), bytes,
+                                  counter.data_ptr<int>(), counter.data_ptr<int>() + 1, mode, current_stream()),
+                "eppgcn_build_part");
+      auto host = counter.cpu();
+      const int parts = host.data_ptr<int>()[0], status = host.data_ptr<int>()[1];
+      if (status == EPP_OK) return {partPtr.narrow(0, 0, parts + 1).clone(), part2Node.narrow(0, 0, parts).clone()};
+      if (mode == 1) epp_check(status, "eppgcn_build_part");      // mode 0 ran out of its bounded wait: repeat without waiting
+    }
+  }
   TORCH_CHECK(indptr.dim() == 1 && indptr.numel() >= 1, "indptr must be a 1-D tensor of num_nodes + 1 entries");
   auto ip = indptr.contiguous();
   const int n = static_cast<int>(ip.numel() - 1);
@@ -544,6 +628,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("get_map_back_part_size", &get_map_back_part_size, "regression rule for the backward part size (CUDA)");
   m.def("split_back_part", &split_back_part, "split active rows into backward parts (CUDA)");
   m.def("get_ginfo", &get_ginfo, "degree histogram features (CPU)");
+  m.def("ours_backward_weight_only", &ours_backward_weight_only,
+        "ours_backward without the input gradient: [empty, d_weight] (not in the reference)");
   m.def("clear_plans", &clear_plans, "drop the aggregation plans the operators keep (not in the reference)");
   m.def("num_plans", &num_plans, "number of aggregation plans currently kept (not in the reference)");
 }

@@ -280,7 +280,8 @@ __global__ void skip_first_ticket_kernel(ScanHeader *hdr) { hdr->ticket = 1u; }
 template <int MODE>
 __global__ void __launch_bounds__(kScanThreads) split_parts_kernel(
     const int *__restrict__ node_deg, int num_nodes, int part_size, int *__restrict__ part_pointer,
-    int out_len, int num_tiles, ScanHeader *hdr, unsigned long long *desc, int *num_parts_dev) {
+    int out_len, int num_tiles, ScanHeader *hdr, unsigned long long *desc, int *num_parts_dev,
+    int *__restrict__ part2node = nullptr, int part2node_len = 0) {
   __shared__ unsigned s_warp[kScanWarps + 1][2];
   __shared__ unsigned s_cpre[kSplitTile + 1];
   __shared__ unsigned s_epre[kSplitTile];
@@ -343,12 +344,19 @@ __global__ void __launch_bounds__(kScanThreads) split_parts_kernel(
     const unsigned k = j - s_cpre[lo];
     const long long slot = static_cast<long long>(pc) + j;
     if (slot < out_len) part_pointer[slot] = static_cast<int>(pe + s_epre[lo] + k * static_cast<unsigned>(part_size));
+    if (part2node && slot < part2node_len) part2node[slot] = tile * kSplitTile + lo;     // the part's vertex
   }
   if (tile == num_tiles - 1 && threadIdx.x == 0) {
     const long long slot = static_cast<long long>(pc) + tot_c;
     if (slot < out_len) part_pointer[slot] = static_cast<int>(pe + tot_d);
     *num_parts_dev = static_cast<int>(pc + tot_c);
   }
+}
+
+// Row lengths of a CSR, the input of the part splitting when it builds the forward groups.
+__global__ void __launch_bounds__(256) row_lengths_kernel(const int *__restrict__ row_ptr, int num_nodes, int *deg) {
+  const int v = blockIdx.x * blockDim.x + threadIdx.x;
+  if (v < num_nodes) deg[v] = __ldg(row_ptr + v + 1) - __ldg(row_ptr + v);
 }
 
 __global__ void __launch_bounds__(256) count_nonzero_kernel(const int *__restrict__ v, long long length, int *count_dev) {
@@ -585,5 +593,66 @@ EPP_EXPORT int eppgcn_count_nonzero(const int *values, int length, int *count_de
   EPP_REQUIRE(values, "null pointer");
   count_nonzero_kernel<<<tail_grid(length), 256, 0, s>>>(values, length, count_dev);
   EPP_CHECK_LAUNCH("count_nonzero_kernel");
+  return EPP_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Neighbour groups on the device.  build_part (EPPGCN.cpp:186-227) and the
+// part splitting compute the same thing from different inputs: a vertex with d
+// edges yields ceil(d / part_size) consecutive pieces of its edge range.  With
+// the row lengths of the CSR as "node degrees", the splitting kernel's part
+// pointers are the group pointers (edge offsets equal CSR offsets), and the
+// vertex it finds for every slot is part2Node.
+// ---------------------------------------------------------------------------
+EPP_EXPORT size_t eppgcn_build_part_scratch_bytes(int num_nodes) {
+  const size_t n = num_nodes < 0 ? 0 : static_cast<size_t>(num_nodes);
+  return (eppgcn_split_scratch_bytes(num_nodes) + 255) / 256 * 256 + sizeof(int) * (n + 1);
+}
+
+EPP_EXPORT int eppgcn_build_part(const int *row_ptr, int num_nodes, int part_size, int *part_ptr, int part_ptr_len,
+                                 int *part2node, int part2node_len, void *scratch, size_t scratch_bytes,
+                                 int *num_parts_dev, int *status_dev, int mode, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EPP_REQUIRE(num_nodes >= 0 && part_ptr_len >= 0 && part2node_len >= 0, "negative size");
+  EPP_REQUIRE(part_size >= 1, "part size must be >= 1");
+  EPP_REQUIRE(num_parts_dev && status_dev, "null result pointer");
+  EPP_REQUIRE(mode == 0 || mode == 1, "mode must be 0 or 1");
+  EPP_CUDA_TRY(cudaMemsetAsync(num_parts_dev, 0, sizeof(int), s));
+  EPP_CUDA_TRY(cudaMemsetAsync(status_dev, 0, sizeof(int), s));
+  EPP_REQUIRE(part_ptr_len == 0 || part_ptr, "null pointer");
+  EPP_REQUIRE(part2node_len == 0 || part2node, "null pointer");
+  if (num_nodes == 0) {
+    if (part_ptr_len) EPP_CUDA_TRY(cudaMemsetAsync(part_ptr, 0, sizeof(int) * static_cast<size_t>(part_ptr_len), s));
+    return EPP_OK;
+  }
+  EPP_REQUIRE(row_ptr && scratch, "null pointer");
+  EPP_REQUIRE(scratch_bytes >= eppgcn_build_part_scratch_bytes(num_nodes), "scratch too small");
+  EPP_REQUIRE(reinterpret_cast<uintptr_t>(scratch) % 8 == 0, "scratch must be 8-byte aligned");
+  const size_t scan_bytes = (eppgcn_split_scratch_bytes(num_nodes) + 255) / 256 * 256;
+  int *deg = reinterpret_cast<int *>(static_cast<char *>(scratch) + scan_bytes);
+  row_lengths_kernel<<<static_cast<unsigned>(ceil_div_ll(num_nodes, 256)), 256, 0, s>>>(row_ptr, num_nodes, deg);
+  EPP_CHECK_LAUNCH("row_lengths_kernel");
+  const int tiles = static_cast<int>(ceil_div_ll(num_nodes, kSplitTile));
+  ScanHeader *hdr = static_cast<ScanHeader *>(scratch);
+  unsigned long long *desc = reinterpret_cast<unsigned long long *>(hdr + 1);
+  EPP_CUDA_TRY(cudaMemsetAsync(scratch, 0, scan_scratch_bytes(tiles), s));
+  if (mode == 0) {
+    split_parts_kernel<kLookback><<<tiles, kScanThreads, 0, s>>>(deg, num_nodes, part_size, part_ptr, part_ptr_len,
+                                                                 tiles, hdr, desc, num_parts_dev, part2node,
+                                                                 part2node_len);
+    EPP_CHECK_LAUNCH("split_parts_kernel<lookback, groups>");
+  } else {
+    split_parts_kernel<kCountOnly><<<tiles, kScanThreads, 0, s>>>(deg, num_nodes, part_size, part_ptr, part_ptr_len,
+                                                                  tiles, hdr, desc, num_parts_dev);
+    EPP_CHECK_LAUNCH("split_parts_kernel<count>");
+    scan_tiles_kernel<<<1, 1024, 0, s>>>(desc, tiles);
+    EPP_CHECK_LAUNCH("scan_tiles_kernel");
+    split_parts_kernel<kGivenOffsets><<<tiles, kScanThreads, 0, s>>>(deg, num_nodes, part_size, part_ptr,
+                                                                     part_ptr_len, tiles, hdr, desc, num_parts_dev,
+                                                                     part2node, part2node_len);
+    EPP_CHECK_LAUNCH("split_parts_kernel<scatter, groups>");
+  }
+  publish_status_kernel<<<1, 1, 0, s>>>(hdr, status_dev);
+  EPP_CHECK_LAUNCH("publish_status_kernel");
   return EPP_OK;
 }

@@ -74,6 +74,7 @@ struct eppgcn_tile_plan {
   int *seg_len;     // [num_ranks] build-time: number of edges of the rank
   int *zero_rows;   // [num_zero]  rows cleared before every aggregation
   unsigned char *used;  // [num_sources] 1 where an edge of the list names the source row
+  int *active_rows; // [nonempty_rows] the rows that have edges, ascending
   // host side
   epp::ClassTable table;
   long long num_edges, num_slots;
@@ -357,7 +358,7 @@ PlanBounds plan_bounds(long long num_edges, int num_rows) {
   return b;
 }
 struct PlanLayout {
-  size_t slots, row_of, seg_start, seg_len, zero_rows, used, total;
+  size_t slots, row_of, seg_start, seg_len, zero_rows, used, active_rows, total;
 };
 PlanLayout plan_layout(long long num_edges, int num_rows, int num_sources) {
   const PlanBounds b = plan_bounds(num_edges, num_rows);
@@ -369,6 +370,7 @@ PlanLayout plan_layout(long long num_edges, int num_rows, int num_sources) {
   l.seg_len = off;   off += round256(4 * b.ranks);
   l.zero_rows = off; off += round256(4 * (static_cast<size_t>(num_rows) + 1));
   l.used = off;      off += round256(static_cast<size_t>(num_sources) + 1);
+  l.active_rows = off; off += round256(4 * (static_cast<size_t>(num_rows) + 1));
   l.total = off;
   return l;
 }
@@ -399,6 +401,7 @@ int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, con
   p->seg_len = reinterpret_cast<int *>(base + l.seg_len);
   p->zero_rows = reinterpret_cast<int *>(base + l.zero_rows);
   p->used = reinterpret_cast<unsigned char *>(base + l.used);
+  p->active_rows = reinterpret_cast<int *>(base + l.active_rows);
   p->num_edges = num_edges;
   p->num_rows = num_rows;
   p->num_sources = num_sources;
@@ -490,6 +493,12 @@ int build_plan(eppgcn_tile_plan **out_plan, void *dev_buf, size_t dev_bytes, con
   if (!zero_rows.empty())
     EPP_CUDA_TRY(cudaMemcpyAsync(p->zero_rows, zero_rows.data(), sizeof(int) * zero_rows.size(),
                                  cudaMemcpyHostToDevice, s));
+  std::vector<int> active;
+  active.reserve(segs.size());
+  for (int r = 0; r < num_rows; ++r)
+    if (has_edges[r]) active.push_back(r);
+  if (!active.empty())
+    EPP_CUDA_TRY(cudaMemcpyAsync(p->active_rows, active.data(), sizeof(int) * active.size(), cudaMemcpyHostToDevice, s));
   EPP_CUDA_TRY(cudaMemsetAsync(p->used, 0, static_cast<size_t>(num_sources) + 1, s));
   for (int i = 0; i < t.count; ++i) {
     const long long slots = t.slot_off[i + 1] - t.slot_off[i];
@@ -620,6 +629,13 @@ EPP_EXPORT int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *ou
   EPP_REQUIRE(plan && out8, "null pointer");
   out8[0] = plan->num_edges; out8[1] = plan->num_rows; out8[2] = plan->num_slots; out8[3] = plan->num_ranks;
   out8[4] = plan->nonempty_rows; out8[5] = plan->num_zero; out8[6] = plan->hub_rows; out8[7] = plan->zero_all;
+  return EPP_OK;
+}
+
+EPP_EXPORT int eppgcn_tile_plan_active_rows(const eppgcn_tile_plan *plan, const int **rows_dev, int *count) {
+  EPP_REQUIRE(plan && rows_dev && count, "null pointer");
+  *rows_dev = plan->active_rows;
+  *count = plan->nonempty_rows;
   return EPP_OK;
 }
 

@@ -12,7 +12,7 @@
 // A block owns 128 rows.  X is streamed through shared memory in chunks of 32
 // columns with cp.async (two buffers); the matching 32 rows of W ride along.
 // A thread accumulates a 4x4 tile: four rows times four output columns.
-#include "common.cuh"
+#include "rowio.cuh"
 
 namespace epp {
 namespace {
@@ -201,6 +201,7 @@ namespace {
 template <int DP>
 __global__ void __launch_bounds__(256) weight_grad_kernel(float *__restrict__ dw, const float *__restrict__ x,
                                                           long long ldx, const float *__restrict__ d, long long ldd,
+                                                          const int *__restrict__ row_list,
                                                           int n, int k, int dout, int rows_per_block,
                                                           int kWgRows) {
   extern __shared__ __align__(16) float wg_smem[];
@@ -231,8 +232,9 @@ __global__ void __launch_bounds__(256) weight_grad_kernel(float *__restrict__ dw
       const int dr = blockDim.x / tk, dp = blockDim.x % tk;
       int r = threadIdx.x / tk, piece = threadIdx.x % tk;
       while (r < kWgRows) {
-        const long long row = r0 + r;
-        stage4(xb + r * kp + piece * 4, x + row * ldx + piece * 4, row < row_end ? min(4, k - piece * 4) : 0, align_x);
+        const long long at = r0 + r;                 // position in the walk; the row itself may come from the list
+        const long long row = (row_list && at < row_end) ? __ldg(row_list + at) : at;
+        stage4(xb + r * kp + piece * 4, x + row * ldx + piece * 4, at < row_end ? min(4, k - piece * 4) : 0, align_x);
         r += dr;
         piece += dp;
         if (piece >= tk) { piece -= tk; ++r; }
@@ -240,9 +242,10 @@ __global__ void __launch_bounds__(256) weight_grad_kernel(float *__restrict__ dw
     }
     for (int i = threadIdx.x; i < kWgRows * TX; i += blockDim.x) {
       const int r = i / TX, piece = i % TX;
-      const long long row = r0 + r;
+      const long long at = r0 + r;
+      const long long row = (row_list && at < row_end) ? __ldg(row_list + at) : at;
       float *dst = db + r * DP + piece * 4;
-      stage4(dst, d + row * ldd + piece * 4, row < row_end ? min(4, dout - piece * 4) : 0, align_d);
+      stage4(dst, d + row * ldd + piece * 4, at < row_end ? min(4, dout - piece * 4) : 0, align_d);
     }
     cp_commit();
   };
@@ -294,25 +297,22 @@ __global__ void __launch_bounds__(256) weight_grad_kernel(float *__restrict__ dw
 }
 
 template <int DP>
-int launch_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd, int n, int k, int dout,
-                       cudaStream_t s) {
+int launch_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd, const int *row_list,
+                       int n, int k, int dout, cudaStream_t s) {
   const int kp = (k + 3) / 4 * 4;
   int kWgRows = 36 * 1024 / ((kp + DP) * static_cast<int>(sizeof(float)));
   kWgRows = kWgRows < 32 ? 32 : (kWgRows > 512 ? 512 : kWgRows / 32 * 32);
   const int smem = 2 * kWgRows * (kp + DP) * static_cast<int>(sizeof(float));
-  static int configured = 0;
-  if (smem > 48 * 1024 && configured < smem) {
-    EPP_CUDA_TRY(cudaFuncSetAttribute(weight_grad_kernel<DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured = smem;
-  }
-  int dev = 0, sms = 148;
-  EPP_CUDA_TRY(cudaGetDevice(&dev));
-  EPP_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  static SmemOptIn memo;                         // per instantiation; remembers the opt-in per device
+  if (const int rc = smem_opt_in(memo, reinterpret_cast<const void *>(weight_grad_kernel<DP>), smem); rc != EPP_OK)
+    return rc;
+  int sms = 148;
+  if (const int rc = device_sm_count(&sms); rc != EPP_OK) return rc;
   long long blocks = static_cast<long long>(sms) * 4;
   long long rows_per_block = ceil_div_ll(ceil_div_ll(n, blocks), kWgRows) * kWgRows;
   if (rows_per_block < kWgRows) rows_per_block = kWgRows;
   blocks = ceil_div_ll(n, rows_per_block);
-  weight_grad_kernel<DP><<<static_cast<unsigned>(blocks), 256, smem, s>>>(dw, x, ldx, d, ldd, n, k, dout,
+  weight_grad_kernel<DP><<<static_cast<unsigned>(blocks), 256, smem, s>>>(dw, x, ldx, d, ldd, row_list, n, k, dout,
                                                                           static_cast<int>(rows_per_block), kWgRows);
   EPP_CHECK_LAUNCH("weight_grad_kernel");
   return EPP_OK;
@@ -321,8 +321,8 @@ int launch_weight_grad(float *dw, const float *x, long long ldx, const float *d,
 }  // namespace
 }  // namespace epp
 
-EPP_EXPORT int eppgcn_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd,
-                                  int num_rows, int k, int dout, void *stream) {
+static int weight_grad_impl(float *dw, const float *x, long long ldx, const float *d, long long ldd,
+                            const int *row_list, int num_rows, int k, int dout, void *stream) {
   using namespace epp;
   EPP_REQUIRE(num_rows >= 0 && k >= 1 && dout >= 1, "negative size, k < 1 or dout < 1");
   const int dp = (dout + 3) / 4 * 4;
@@ -339,13 +339,27 @@ EPP_EXPORT int eppgcn_weight_grad(float *dw, const float *x, long long ldx, cons
   EPP_REQUIRE(reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(d) % 16 == 0,
               "x and d must be 16-byte aligned");
   switch (dp) {
-    case 4:  return launch_weight_grad<4>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 8:  return launch_weight_grad<8>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 12: return launch_weight_grad<12>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 16: return launch_weight_grad<16>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 20: return launch_weight_grad<20>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 24: return launch_weight_grad<24>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    case 28: return launch_weight_grad<28>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
-    default: return launch_weight_grad<32>(dw, x, ldx, d, ldd, num_rows, k, dout, s);
+    case 4:  return launch_weight_grad<4>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 8:  return launch_weight_grad<8>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 12: return launch_weight_grad<12>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 16: return launch_weight_grad<16>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 20: return launch_weight_grad<20>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 24: return launch_weight_grad<24>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    case 28: return launch_weight_grad<28>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
+    default: return launch_weight_grad<32>(dw, x, ldx, d, ldd, row_list, num_rows, k, dout, s);
   }
+}
+
+EPP_EXPORT int eppgcn_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd,
+                                  int num_rows, int k, int dout, void *stream) {
+  return weight_grad_impl(dw, x, ldx, d, ldd, nullptr, num_rows, k, dout, stream);
+}
+
+EPP_EXPORT int eppgcn_weight_grad_rows(float *dw, const float *x, long long ldx, const float *d, long long ldd,
+                                       const int *rows, int num_listed, int k, int dout, void *stream) {
+  if (num_listed > 0 && !rows) {
+    epp::set_error("eppgcn_weight_grad_rows: null row list");
+    return EPP_ERR_BAD_ARG;
+  }
+  return weight_grad_impl(dw, x, ldx, d, ldd, num_listed > 0 ? rows : nullptr, num_listed, k, dout, stream);
 }

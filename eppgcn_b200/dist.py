@@ -339,6 +339,7 @@ class DealtHalo:
         self.rank, self.world, self.group, self.n_loc = rank, world, group, n_loc
         self.fabric = fabric if world > 1 else None
         self.overlap, self._side = False, None       # push chunk c+1 on a side stream beside the aggregation of chunk c
+        self.lead_barrier = False                    # True: always wait for the readers before a push (see start)
         ids = cols.long()
         v0 = rank * n_loc
         own = (ids >= v0) & (ids < v0 + n_loc)
@@ -435,7 +436,7 @@ class DealtHalo:
             # (layers of different width, forward and backward) therefore pays one barrier per aggregation.
             key = (d, len(bufs))
             stamp = self._stamps.get(key)
-            if stamp is None or self.fabric.count <= stamp or (self.overlap and len(bufs) > 1):
+            if self.lead_barrier or stamp is None or self.fabric.count <= stamp or (self.overlap and len(bufs) > 1):
                 self.fabric.barrier()
             if local is not None:
                 for c, (_, buf) in enumerate(bufs):
@@ -588,7 +589,10 @@ class DistHotPath:
         self.part_size = max(int(ds.avg_degree), 1)
         L = ds.num_layers
         row_cpu = sh.indptr if on_device else torch.from_numpy(sh.indptr)
-        pp, p2n = gnna.build_part(self.part_size, row_cpu)
+        if on_device:         # the graph never left the GPU: its groups are built there too
+            pp, p2n = capi.build_part_device(self.part_size, local_ptr, sh.num_edges)
+        else:
+            pp, p2n = gnna.build_part(self.part_size, row_cpu)
         self.row = row_cpu.to(dev)
         self.col = sh.indices if on_device else torch.from_numpy(sh.indices).to(dev)
         self.pp, self.p2n = pp.to(dev), p2n.to(dev)

@@ -41,8 +41,13 @@ class GNNAFunction(torch.autograd.Function):
     def backward(ctx, d_output):
         X, weight = ctx.saved_tensors
         b = ctx.backInfo
-        d_input, d_weight = GNNA.ours_backward(d_output, X, weight, b.id, b.partPointer, b.edgeList, b.degrees,
-                                               b.partSize, b.numParts, b.layer, b.blockx, b.blocky)
+        args = (d_output, X, weight, b.id, b.partPointer, b.edgeList, b.degrees, b.partSize, b.numParts, b.layer,
+                b.blockx, b.blocky)
+        if not ctx.needs_input_grad[0] and hasattr(GNNA, "ours_backward_weight_only"):
+            # the input is the feature matrix (first layer): its gradient, an [N, Din] product the
+            # reference computes regardless (EPPGCN_kernel.cu:614), is never used
+            return None, GNNA.ours_backward_weight_only(*args)[1], None, None, None, None, None
+        d_input, d_weight = GNNA.ours_backward(*args)
         return d_input, d_weight, None, None, None, None, None
 
 

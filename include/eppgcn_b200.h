@@ -155,6 +155,8 @@ int eppgcn_tile_plan_from_ids(eppgcn_tile_plan **plan, void *dev_buf, size_t dev
                               int num_sources, void *stream);
 void eppgcn_tile_plan_destroy(eppgcn_tile_plan *plan);
 int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *out8);
+/* The rows that have at least one edge, ascending (device int32 inside the plan's buffer). */
+int eppgcn_tile_plan_active_rows(const eppgcn_tile_plan *plan, const int **rows_dev, int *count);
 int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src, long long src_ld,
                       const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream);
 int eppgcn_pack_scaled_rows(float *dst, long long dst_ld, const float *x, long long ldx,
@@ -198,6 +200,13 @@ int eppgcn_update_scaled(float *out, long long ld_out, const float *x, long long
  */
 int eppgcn_weight_grad(float *dw, const float *x, long long ldx, const float *d, long long ldd,
                        int num_rows, int k, int dout, void *stream);
+/* The same product over a list of rows only,  dw = sum over i < num_listed of
+ * x[rows[i]]^T d[rows[i]]  -- the masked product the reference sketches at
+ * EPPGCN/GCNConv/EPPGCN_kernel.cu:607,616.  With the rows of a layer's
+ * execution path (eppgcn_tile_plan_active_rows) the rows of x that face an
+ * all-zero row of d are never read.  rows: device int32. */
+int eppgcn_weight_grad_rows(float *dw, const float *x, long long ldx, const float *d, long long ldd,
+                            const int *rows, int num_listed, int k, int dout, void *stream);
 
 /* ------------------------------------------------------------------------
  * Execution-path marking for one preparation step.
@@ -302,6 +311,23 @@ int eppgcn_split_parts(const int *node_deg, int num_nodes, int part_size,
                        int *part_pointer, int out_len,
                        void *scratch, size_t scratch_bytes,
                        int *num_parts_dev, int *status_dev, int mode, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Neighbour groups built on the device: the same partition as
+ * eppgcn_build_part_host / build_part (EPPGCN/GCNConv/EPPGCN.cpp:186-227) from a
+ * row pointer that already lives in device memory, in one launch (plus a
+ * row-length pass), int32-exact for any offsets.  For every vertex with d > 0
+ * edges, ceil(d / part_size) groups: part_ptr[g] is the group's first edge,
+ * part2node[g] its vertex, part_ptr[num_parts] = row_ptr[num_nodes].
+ * part_ptr_len / part2node_len are the capacities of the two outputs (entries
+ * beyond them are dropped; ceil(E / part_size) + num_nodes + 1 always
+ * suffices); *num_parts_dev receives the group count.  scratch / status / mode
+ * as for eppgcn_split_parts, sized by eppgcn_build_part_scratch_bytes.
+ */
+size_t eppgcn_build_part_scratch_bytes(int num_nodes);
+int eppgcn_build_part(const int *row_ptr, int num_nodes, int part_size, int *part_ptr, int part_ptr_len,
+                      int *part2node, int part2node_len, void *scratch, size_t scratch_bytes,
+                      int *num_parts_dev, int *status_dev, int mode, void *stream);
 
 /* Number of non-zero entries, stored to *count_dev.
  * Replaces compact_count (EPPGCN/GCNConv/cuCompactor.cu:638-678, :694-696). */

@@ -148,3 +148,32 @@ def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable(cuda):
     for mode in (1, 0):
         ids, edges, valid = capi.compact_mask(t(mask, cuda), t(col, cuda), mode)
         assert valid == want[2] and np.array_equal(ids.cpu().numpy(), want[0])
+
+
+@pytest.mark.parametrize("part_size", [1, 3, 17, 64, 100_000])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_groups_built_on_the_device_equal_the_host_partition(cuda, part_size, mode):
+    """eppgcn_build_part against eppgcn_build_part_host and the oracle: empty rows, an empty last
+    vertex, hub rows of thousands of groups, more than one scan tile."""
+    import eppgcn_b200
+    rng = np.random.Generator(np.random.PCG64(part_size))
+    deg = rng.poisson(3.0, 70_001)
+    deg[rng.random(deg.size) < 0.3] = 0
+    deg[[5, 40_000, 69_999]] = [30_000, 77_777, 12_345]
+    deg[-1] = 0
+    indptr = np.zeros(deg.size + 1, dtype=np.int32)
+    np.cumsum(deg, out=indptr[1:])
+    want_pp, want_p2n = O.build_part(part_size, indptr)
+    host_pp, host_p2n = capi.build_part(part_size, torch.from_numpy(indptr))
+    assert np.array_equal(host_pp.numpy(), want_pp) and np.array_equal(host_p2n.numpy(), want_p2n)
+    pp, p2n = capi.build_part_device(part_size, torch.from_numpy(indptr).to(cuda), mode=mode)
+    assert np.array_equal(pp.cpu().numpy(), want_pp) and np.array_equal(p2n.cpu().numpy(), want_p2n)
+    if mode == 0:                                   # the operator accepts a CUDA row pointer as well
+        gnna = eppgcn_b200.load_gnnadvisor()
+        a, b = gnna.build_part(part_size, torch.from_numpy(indptr).to(cuda))
+        assert a.is_cuda and torch.equal(a, pp) and torch.equal(b, p2n)
+
+
+def test_groups_of_an_empty_graph_on_the_device(cuda):
+    pp, p2n = capi.build_part_device(4, torch.zeros(11, dtype=torch.int32, device=cuda))
+    assert pp.tolist() == [0] and p2n.numel() == 0

@@ -249,3 +249,59 @@ def test_results_land_in_a_column_block_of_a_wider_matrix(cuda, dim, left, right
     want = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, feat, conv["numParts"])
     assert_close(got[:, left:left + dim], want, what="backward column block")
     assert (got[:, :left] == 7.0).all() and (got[:, left + dim:] == 7.0).all()
+
+
+def test_weight_grad_over_the_rows_of_a_path(cuda):
+    """X^T d' restricted to the rows that have edges in a plan: d' is zero everywhere else, so the
+    product equals the one over all rows."""
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    conv = make_path(indptr, indices, 0.05, 2, 6, 8, seed=4)[1]
+    plan = capi.TilePlan.from_ids(t(conv["id"], cuda), t(conv["edgeList"], cuda), conv["valid_len"], n)
+    active = conv["node_degs"] > 0
+    assert 0 < active.sum() < n
+    rng = np.random.Generator(np.random.PCG64(8))
+    for k, dout in ((128, 16), (16, 22), (12, 5)):
+        x = rng.standard_normal((n, k)).astype(np.float32)
+        d = rng.standard_normal((n, dout)).astype(np.float32)
+        d[~active] = 0.0
+        got = capi.weight_grad(t(x, cuda), t(d, cuda), plan).cpu().numpy()
+        want = x.astype(np.float64).T @ d.astype(np.float64)
+        mag = np.abs(x.astype(np.float64)).T @ np.abs(d.astype(np.float64))
+        assert np.all(np.abs(got - want) <= 1e-6 + 1e-6 * mag * max(1.0, np.sqrt(n) / 8)), f"k {k} dout {dout}"
+        # rows off the list are not read at all: poison them
+        x[~active] = np.nan
+        got = capi.weight_grad(t(x, cuda), t(d, cuda), plan).cpu().numpy()
+        assert np.isfinite(got).all()
+
+
+@pytest.mark.parametrize("din,dout", [(128, 64), (64, 64), (64, 32), (40, 36)])
+def test_operator_handles_wide_layers_without_library_gemms(cuda, din, dout):
+    """forward and ours_backward for layers wider than one 32-column block (the 3-layer configuration:
+    128 -> 64 -> 64 -> 32): update, d_input and d_weight go through this library's FMA kernels block
+    by block and match float64."""
+    import eppgcn_b200
+    gnna = eppgcn_b200.load_gnnadvisor()
+    indptr, indices = random_csr(**GRAPHS["hubs"])
+    n = len(indptr) - 1
+    deg = degrees_of(indptr)
+    rng = np.random.Generator(np.random.PCG64(din + dout))
+    x = rng.standard_normal((n, din)).astype(np.float32)
+    w = rng.uniform(-0.3, 0.3, (din, dout)).astype(np.float32)
+    pp, p2n = O.build_part(6, indptr)
+    y = gnna.forward(t(x, cuda), t(w, cuda), t(indptr, cuda), t(indices, cuda), t(deg, cuda), t(pp, cuda),
+                     t(p2n, cuda), 6, 32, 8)[0]
+    assert_close(y.cpu().numpy(), O.gcn_layer_forward(x, w, indptr, indices, deg), 4e-5, 4e-6, f"forward {din}->{dout}")
+    d_out = rng.standard_normal((n, dout)).astype(np.float32)
+    conv = make_path(indptr, indices, 0.2, 1, 6, 8, seed=din)[0]
+    args = (t(d_out, cuda), t(x, cuda), t(w, cuda), t(conv["id"], cuda), t(conv["partPointer"], cuda),
+            t(conv["edgeList"], cuda), t(deg, cuda), 8, conv["numParts"], 1, 4, 16)
+    d_in, d_w = gnna.ours_backward(*args)
+    wi, ww, _ = O.gcn_layer_backward(d_out, x, w, conv["id"], conv["partPointer"], conv["edgeList"], deg,
+                                     conv["numParts"])
+    assert_close(d_in.cpu().numpy(), wi, 4e-5, 4e-6, f"d_input {din}->{dout}")
+    s = float(np.abs(ww).max())
+    assert_close(d_w.cpu().numpy() / s, ww / s, 1e-4, 1e-5, f"d_weight {din}->{dout}")
+    none, d_w2 = gnna.ours_backward_weight_only(*args)
+    assert none.numel() == 0
+    assert_close(d_w2.cpu().numpy() / s, ww / s, 1e-4, 1e-5, f"d_weight (weight only) {din}->{dout}")

@@ -19,6 +19,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB_NAME = "libeppgcn_b200.so"
 LIB_PATH = os.path.join(HERE, LIB_NAME)
+DEBUG_LIB_PATH = os.path.join(HERE, "libeppgcn_b200_debug.so")
 PROBE_PATH = os.path.join(HERE, "libeppgcn_probe.so")
 EXT_NAME = "GNNAdvisor"
 EXT_PATH = os.path.join(HERE, EXT_NAME + sysconfig.get_config_var("EXT_SUFFIX"))
@@ -52,16 +53,22 @@ def _run(cmd: list[str], verbose: bool):
         print(r.stdout + r.stderr, flush=True)
 
 
-def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False) -> str:
+def build_library(force: bool = False, verbose: bool = False, ptxas_info: bool = False,
+                  debug_bounds: bool = False) -> str:
+    """``debug_bounds``: the bounds-checking build (``-DEPP_DEBUG_BOUNDS``) as a library of its own,
+    ``libeppgcn_b200_debug.so``, which ``capi`` loads when ``EPPGCN_B200_DEBUG_BOUNDS=1`` is set."""
     srcs = [os.path.join(CSRC, s) for s in LIB_SOURCES]
     deps = srcs + [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "rowio.cuh"),
                    os.path.join(HERE, "..", "include", "eppgcn_b200.h"), __file__]
-    if force or _stale(LIB_PATH, deps):
+    target = DEBUG_LIB_PATH if debug_bounds else LIB_PATH
+    if force or _stale(target, deps):
         flags = list(NVCC_FLAGS)
         if ptxas_info:
             flags += ["-Xptxas", "-v"]
-        _run([_nvcc(), *flags, "-shared", "-o", LIB_PATH, *srcs], verbose or ptxas_info)
-    return LIB_PATH
+        if debug_bounds:
+            flags += ["-DEPP_DEBUG_BOUNDS"]
+        _run([_nvcc(), *flags, "-shared", "-o", target, *srcs], verbose or ptxas_info)
+    return target
 
 
 def build_probe(force: bool = False, verbose: bool = False) -> str:
@@ -109,3 +116,5 @@ def build_all(force: bool = False, verbose: bool = False):
 
 if __name__ == "__main__":
     build_all(force="--force" in sys.argv, verbose=True)
+    if "--debug-bounds" in sys.argv:
+        build_library(force="--force" in sys.argv, verbose=True, debug_bounds=True)

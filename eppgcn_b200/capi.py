@@ -12,7 +12,10 @@ import os
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libeppgcn_b200.so")
+# EPPGCN_B200_DEBUG_BOUNDS=1 selects the bounds-checking build of the library
+# (``python -m eppgcn_b200.build --debug-bounds``), see eppgcn_debug_status.
+DEBUG_BOUNDS = os.environ.get("EPPGCN_B200_DEBUG_BOUNDS", "") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "libeppgcn_b200_debug.so" if DEBUG_BOUNDS else "libeppgcn_b200.so")
 
 EPP_OK, EPP_ERR_BAD_ARG, EPP_ERR_CUDA, EPP_ERR_SCAN_TIMEOUT, EPP_ERR_TOO_LARGE, EPP_ERR_PEER_TIMEOUT = range(6)
 
@@ -32,6 +35,7 @@ SIGNATURES = {
     "eppgcn_tile_plan_destroy": (None, [_P]),
     "eppgcn_tile_plan_info": (_I, [_P, _P]),
     "eppgcn_spmm_tiles": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
+    "eppgcn_debug_status": (_I, [_P, _I]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
     "eppgcn_weight_grad_rows": (_I, [_P, _P, _LL, _P, _LL, _P, _I, _I, _I, _P]),
@@ -246,6 +250,14 @@ def pack_scaled_rows(x, scale, plan=None, out=None, pad_to=8):
                                         None if scale is None else _dev(scale, torch.float32, "scale"),
                                         None if plan is None else plan._handle, n, dim, _stream()))
     return out
+
+
+def debug_status(reset=True):
+    """``(code, value, limit, tile)`` of the bounds-checking build: code 0 nothing found, 1 source id,
+    2 row id out of range, -1 not a bounds-checking build."""
+    out = (_I * 4)()
+    check(lib().eppgcn_debug_status(out, 1 if reset else 0))
+    return tuple(out)
 
 
 def spmm_tiles(src, plan, row_scale=None, out=None):

@@ -95,8 +95,22 @@ struct TileArgs {
   int num_tiles;
   int dim;                        // columns handled by this launch
   int lanes;                      // lanes per row, ceil(dim / 4)
+  int num_rows, num_sources;      // limits of the ids (looked at by the bounds-checking build only)
   ClassTable t;
 };
+
+// Bounds-checking build (-DEPP_DEBUG_BOUNDS), the stand-in for a memory checker: every source id and
+// every row id is compared with its limit before it is used; an offender is not dereferenced, the
+// first one is recorded here ({code, value, limit, tile}; code 1 = source id, 2 = row id) and the
+// kernel carries on.  eppgcn_debug_status returns the record.
+#ifdef EPP_DEBUG_BOUNDS
+__device__ int g_debug_record[4];
+__device__ __forceinline__ void debug_report(int code, int value, int limit, int tile) {
+  if (atomicCAS(&g_debug_record[0], 0, code) == 0) {
+    g_debug_record[1] = value; g_debug_record[2] = limit; g_debug_record[3] = tile;
+  }
+}
+#endif
 
 __device__ __forceinline__ void load8(const int *p, int (&c)[8]) {
   const int4 a = __ldg(reinterpret_cast<const int4 *>(p));
@@ -115,6 +129,12 @@ __device__ __forceinline__ void put_row(const TileArgs &a, float *out_lane, int 
                                         bool has_cols) {
   if (rid == -1 || !has_cols) return;
   const int row = static_cast<int>(static_cast<unsigned>(rid) & ~kAtomicBit);
+#ifdef EPP_DEBUG_BOUNDS
+  if (row >= a.num_rows) {
+    debug_report(2, row, a.num_rows, -1);
+    return;
+  }
+#endif
   const float s = a.row_scale ? __ldg(a.row_scale + row) : 1.f;
   const float val[4] = {acc[0] * s, acc[1] * s, acc[2] * s, acc[3] * s};
   float *dst = out_lane + static_cast<long long>(row) * a.out_ld;
@@ -178,10 +198,17 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kerne
     float4 v[8];
     auto gather = [&]() {
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < 8; ++u) {
+#ifdef EPP_DEBUG_BOUNDS
+        if (c[u] >= a.num_sources) {
+          debug_report(1, c[u], a.num_sources, tile);
+          c[u] = -1;                               // treated as padding: neither loaded nor added
+        }
+#endif
         if (c[u] >= 0)
           v[u] = __ldg(reinterpret_cast<const float4 *>(
               glane + static_cast<unsigned long long>(static_cast<unsigned>(c[u])) * ld_bytes));
+      }
     };
     auto prefetch_next = [&]() {
       if (next < a.num_tiles) {
@@ -191,8 +218,14 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kerne
     };
     if (pos.width >= 8) {
       // one row per sub-warp, width/8 batches; the row's factor is asked for before the first batch
-      const int rid = rid_wide;
+      int rid = rid_wide;
       const int row = static_cast<int>(static_cast<unsigned>(rid) & ~kAtomicBit);
+#ifdef EPP_DEBUG_BOUNDS
+      if (rid != -1 && row >= a.num_rows) {
+        debug_report(2, row, a.num_rows, tile);
+        rid = -1;
+      }
+#endif
       const float scale = (rid != -1 && a.row_scale) ? __ldg(a.row_scale + row) : 1.f;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       const int *cp = a.slots + pos.slot;
@@ -676,8 +709,25 @@ EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src,
     a.out = out + col0; a.out_ld = out_ld; a.src = src + col0; a.src_ld = src_ld;
     a.slots = plan->slots; a.row_of = plan->row_of; a.row_scale = row_scale;
     a.dim = dim - col0 < 128 ? dim - col0 : 128; a.lanes = lanes_for_dim(a.dim); a.t = plan->table;
+    a.num_rows = plan->num_rows; a.num_sources = plan->num_sources;
     const int rc = ovec == 4 ? launch_tiles<4>(a, s) : ovec == 2 ? launch_tiles<2>(a, s) : launch_tiles<1>(a, s);
     if (rc != EPP_OK) return rc;
   }
+  return EPP_OK;
+}
+
+EPP_EXPORT int eppgcn_debug_status(int *out4, int reset) {
+  EPP_REQUIRE(out4, "null pointer");
+#ifdef EPP_DEBUG_BOUNDS
+  EPP_CUDA_TRY(cudaDeviceSynchronize());
+  EPP_CUDA_TRY(cudaMemcpyFromSymbol(out4, g_debug_record, sizeof(int) * 4));
+  if (reset) {
+    const int zero[4] = {0, 0, 0, 0};
+    EPP_CUDA_TRY(cudaMemcpyToSymbol(g_debug_record, zero, sizeof(zero)));
+  }
+#else
+  (void)reset;
+  out4[0] = -1; out4[1] = out4[2] = out4[3] = 0;      // not a bounds-checking build
+#endif
   return EPP_OK;
 }

@@ -196,6 +196,27 @@ def all_gather_rows(full: torch.Tensor, local: torch.Tensor, bounds, group=None)
     return full
 
 
+def check_agreement(values: dict, group=None, device=None):
+    """Raises on EVERY rank when the ranks do not hold the same integers: ``values`` maps a name
+    (the same names in the same order on all ranks) to an int.  Used before the first exchange, so
+    that a rank started with another graph, seed, layer count or partition fails with a message
+    that names the field instead of exchanging rows of the wrong shape.  One all-gather of a few
+    64-bit words."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return
+    names = list(values)
+    mine = torch.tensor([int(values[k]) for k in names], dtype=torch.int64, device=device)
+    world = dist.get_world_size(group)
+    got = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(got, mine, group=group)
+    table = torch.stack(got).cpu()
+    for j, name in enumerate(names):
+        col = table[:, j]
+        if not bool((col == col[0]).all()):
+            raise RuntimeError(f"the ranks disagree on {name}: " +
+                               ", ".join(f"rank {r}: {int(v)}" for r, v in enumerate(col.tolist())))
+
+
 def or_reduce_mask(mask: torch.Tensor, group=None):
     """In-place OR of a bool mask over ranks (as a byte MAX)."""
     if dist.get_world_size(group) > 1:
@@ -588,6 +609,13 @@ class DistHotPath:
         self.shard = sh
         self.part_size = max(int(ds.avg_degree), 1)
         L = ds.num_layers
+        # every rank must have cut the same graph the same way before a single row is exchanged
+        check_agreement({"the vertex count": self.n, "the edge count": int(ds.num_edges), "the layer count": L,
+                         "the backward part size": back_size, "the column chunk count": chunks,
+                         "the first partition boundary": int(self.bounds[1]),
+                         "the train-mask size": int(ds.train_mask.sum().item() if torch.is_tensor(ds.train_mask)
+                                                    else np.asarray(ds.train_mask).sum())},
+                        group, dev if torch.device(dev).type == "cuda" else None)
         row_cpu = sh.indptr if on_device else torch.from_numpy(sh.indptr)
         if on_device:         # the graph never left the GPU: its groups are built there too
             pp, p2n = capi.build_part_device(self.part_size, local_ptr, sh.num_edges)

@@ -163,6 +163,17 @@ int eppgcn_pack_scaled_rows(float *dst, long long dst_ld, const float *x, long l
                             const float *scale, const eppgcn_tile_plan *plan, int num_rows, int dim,
                             void *stream);
 
+/* Bounds-checking build (the library compiled with -DEPP_DEBUG_BOUNDS, see
+ * eppgcn_b200/build.py): eppgcn_spmm_tiles compares every source id and row id
+ * of a plan with its limit before using it; an offender is skipped, not
+ * dereferenced, and the first one is recorded.  Synchronises the device and
+ * returns the record {code, value, limit, tile}: code 0 = nothing found, 1 = a
+ * source id beyond num_sources, 2 = a row id beyond num_rows, -1 = this is
+ * not a bounds-checking build.  reset != 0 clears the record.  No counterpart
+ * in the reference (its only check is cudaGetLastError + exit after a launch,
+ * EPPGCN/GCNConv/EPPGCN_kernel.cu:195-199). */
+int eppgcn_debug_status(int *out4, int reset);
+
 /* ------------------------------------------------------------------------
  * Dense update of a layer with the source-side factor folded in.
  * Replaces the torch::mm(input, weight) of the forward wrapper

@@ -171,6 +171,22 @@ def test_agrees_with_the_group_kernel_on_rmat(cuda, dim):
     assert torch.allclose(a, b, rtol=2e-5, atol=2e-6 * scale)
 
 
+def test_small_cases_under_the_bounds_checking_build(cuda):
+    """The library compiled with -DEPP_DEBUG_BOUNDS (the stand-in for a memory checker): clean runs
+    leave its record empty, ids beyond their limit are reported and skipped.  Runs in a child process
+    because the choice of library is made when ``capi`` is imported."""
+    import os
+    import subprocess
+    import sys
+    from eppgcn_b200 import build
+    build.build_library(debug_bounds=True)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, EPPGCN_B200_DEBUG_BOUNDS="1", PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "tests.bounds_cases"], cwd=root, env=env, capture_output=True,
+                       text=True, timeout=300)
+    assert r.returncode == 0 and "bounds cases ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
 @pytest.mark.parametrize("dim", [1, 5, 7, 16, 22, 64])
 @pytest.mark.parametrize("view", ["dense", "column_block"])
 def test_pack_scaled_rows_writes_the_rows_the_path_names(cuda, dim, view):

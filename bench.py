@@ -62,6 +62,17 @@ def measured_peak_gbs():
         return 6650.0, "fallback"
 
 
+L2_FLUSH_BYTES = 256 << 20       # twice the 126 MB L2
+
+
+def l2_policy(n, e, dims):
+    """The ``config.l2`` wording of a workload (the same in both arms) and whether its forward inputs fit
+    the flush size, in which case the GPU arm times every step behind a flush."""
+    fits = min(bytes_forward(n, e, d) for d in dims[:2]) < L2_FLUSH_BYTES
+    return ("L2 flushed (256 MiB written) before every timed step" if fits else
+            "inputs exceed L2: every aggregation reads more than the 126 MB cache holds"), fits
+
+
 def recorded_traffic(kernel_source: str):
     """DRAM bytes per launch from the committed profiler record, valid only while the kernel source it
     was captured at is unchanged: the record, or {}."""
@@ -469,23 +480,39 @@ def run_gpu(args):
             fn()
 
     stream = torch.cuda.current_stream()
+    # Every aggregation of the large workloads reads more than the L2 holds; a small graph would stay
+    # cached from one step to the next, so its steps are timed one by one behind a 256 MiB write.
+    l2_note, fits = l2_policy(n, e, dims)
+    flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device=dev) if fits else None
     # -- whole-step timing (the clock sampler runs from the warm-up to the last per-kernel launch) ----
     with ClockSampler(local) as clocks:
         for _ in range(max(args.warmup, 3)):
             step()
         torch.cuda.synchronize()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        ev0.record(stream)
-        for _ in range(args.steps):
-            step()
-        ev1.record(stream)
-        torch.cuda.synchronize()
-        ms_step = ev0.elapsed_time(ev1) / args.steps
+        if flush is None:
+            torch.cuda.synchronize()
+            ev0.record(stream)
+            for _ in range(args.steps):
+                step()
+            ev1.record(stream)
+            torch.cuda.synchronize()
+            ms_step = ev0.elapsed_time(ev1) / args.steps
+        else:                       # a workload that fits L2: every step starts from a flushed cache
+            pairs = []
+            for _ in range(args.steps):
+                flush.zero_()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream); step(); b.record(stream)
+                pairs.append((a, b))
+            torch.cuda.synchronize()
+            ms_step = statistics.mean(a.elapsed_time(b) for a, b in pairs)
         # -- per-aggregation timing (same launches, one event pair each) ----------
         per = [[] for _ in range(4)]
         for _ in range(args.steps):
             for k, fn in enumerate(fns):
+                if flush is not None:
+                    flush.zero_()
                 a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 a.record(stream); fn(); b.record(stream)
                 per[k].append((a, b))
@@ -636,7 +663,7 @@ def run_gpu(args):
         "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4),
         "higher_is_better": False, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_string(args.workload, spec, n, e, dims, ratio, hp.part_size, args.backsize),
-                   "seed": args.seed, "l2": "inputs exceed L2: each step streams >1 GB of distinct data",
+                   "seed": args.seed, "l2": l2_note,
                    "parallelism": "single GPU",
                    "kernel": "tiled plan (rows in width classes, padded edge copy)" if args.kernel == "tiles"
                              else "neighbour-group kernel"},
@@ -677,7 +704,7 @@ def run_reference(args):
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": workload_string(args.workload, spec, graph.num_nodes, graph.num_edges, dims, ratio,
                                                max(int(ds.avg_degree), 1), args.backsize),
-                   "seed": args.seed, "l2": "inputs exceed L2: each step streams >1 GB of distinct data",
+                   "seed": args.seed, "l2": l2_policy(graph.num_nodes, graph.num_edges, dims)[0],
                    "parallelism": "single GPU",
                    "kernel": "tiled plan (rows in width classes, padded edge copy)" if args.kernel == "tiles"
                              else "neighbour-group kernel"},

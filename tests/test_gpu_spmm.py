@@ -176,7 +176,8 @@ def test_forward_prescaled_rows(cuda, dim):
 
 
 @pytest.mark.parametrize("n,k,dout", [(1, 4, 4), (31, 16, 22), (32, 16, 22), (1000, 128, 16), (5000, 7, 5),
-                                      (100_003, 128, 16), (4097, 128, 32), (70_000, 16, 22)])
+                                      (100_003, 128, 16), (4097, 128, 32), (70_000, 16, 22), (3000, 200, 20),
+                                      (2000, 1000, 4), (999, 22, 16), (777, 40, 28), (50_000, 64, 32), (9, 3, 1)])
 def test_weight_grad(cuda, n, k, dout):
     """X^T d' with FP32 FMA and atomically combined slabs, against float64."""
     rng = np.random.Generator(np.random.PCG64(n + k))

@@ -750,6 +750,13 @@ def main():
     p.add_argument("--lead-barrier", action="store_true",
                    help="balanced_halo, push transport: always wait for the readers of a buffer before pushing into "
                         "it (default: only when no other barrier has passed since it was read)")
+    p.add_argument("--stream", action="store_true",
+                   help="multi-GPU, push transport: push the rows peer by peer on a side stream while the edges of the "
+                        "owners that have landed are aggregated (default: push everything, one barrier, then aggregate)")
+    p.add_argument("--owner-groups", type=int, default=0,
+                   help="multi-GPU streamed exchange: bundle the other ranks' rows into this many groups (0: one per rank)")
+    p.add_argument("--no-graph", action="store_true",
+                   help="multi-GPU: submit every launch of the timed epoch by itself instead of replaying one CUDA graph")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-full-epoch", action="store_true")
     p.add_argument("--no-check", action="store_true")

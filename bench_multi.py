@@ -25,7 +25,8 @@ def count_launches(hp, step):
     that clears the whole result uses a memset, which is not a kernel), plus the clearing kernel of a
     group-kernel call that writes a column block."""
     capi = hp.capi
-    names = ["push_rows", "peer_barrier", "spmm_tiles", "pack_scaled_rows", "spmm_forward", "spmm_backward_compacted"]
+    names = ["push_rows", "peer_barrier", "peer_barrier_counted", "push_rows_signal", "bump_counter", "wait_landed",
+             "spmm_tiles", "spmm_tiles_add", "pack_scaled_rows", "spmm_forward", "spmm_backward_compacted"]
     saved = {n: getattr(capi, n) for n in names}
     count = [0]
 
@@ -130,7 +131,8 @@ def run_bench(args, rank: int, world: int, dev):
     if chunks <= 0:           # measured on the 64/64/32-column workload: two 32-column buffers aggregate faster than one
         chunks = 2 if min(dims) >= 32 and all(d % 8 == 0 for d in dims) else 1
     hp = DistHotPath(ds, dev, rank, world, args.backsize, exchange=mode, chunks=chunks,
-                     transport=getattr(args, "transport", "push"), overlap=getattr(args, "overlap", False))
+                     transport=getattr(args, "transport", "push"), overlap=getattr(args, "overlap", False),
+                     streamed=getattr(args, "stream", False), owner_groups=getattr(args, "owner_groups", 0))
     dealt = mode == "balanced_halo"
     if dealt and getattr(args, "lead_barrier", False):
         for plan in [hp.fwd_plan] + [p["plan"] for p in hp.path]:
@@ -202,11 +204,16 @@ def run_bench(args, rank: int, world: int, dev):
 
     # this library's kernels per epoch, counted on one untimed step by wrapping the C-ABI calls
     launches_per_step = count_launches(hp, step)
+    # The timed step is one CUDA graph of those launches (peer stores and flag barriers included) unless
+    # --no-graph is given: a dozen small submissions per aggregation otherwise let the ranks drift apart on
+    # the host, and every barrier then waits for the slowest submitter.
+    graphed = dealt and not getattr(args, "no_graph", False) and (world == 1 or hp.fabric is not None)
+    run = hp.graphed(step) if graphed else step
 
     stream = torch.cuda.current_stream()
     with B.ClockSampler(dev.index) as clocks:
         for _ in range(max(args.warmup, 3)):
-            step()
+            run()
         torch.cuda.synchronize()
         if hp.fabric is not None:
             hp.fabric.check()
@@ -216,7 +223,7 @@ def run_bench(args, rank: int, world: int, dev):
         dist.barrier()
         ev0.record(stream)
         for _ in range(args.steps):
-            step()
+            run()
         ev1.record(stream)
         torch.cuda.synchronize()
         dist.barrier()
@@ -246,21 +253,46 @@ def run_bench(args, rank: int, world: int, dev):
     host_in = [[torch.empty(x.shape, pin_memory=True).copy_(x) for x in views] for views in staged]
     host_out = [torch.empty(o.shape, pin_memory=True) for o in outs]
 
+    # Copies in, kernels and copies out run on three streams, so that PCIe is busy in both directions while
+    # the exchange and the kernels run; events carry the dependencies, including the reuse of the staging
+    # rows (an aggregation's input rows are overwritten only after the kernels that read them).
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    nops = len(ops)
+    staged_ev = [torch.cuda.Event() for _ in range(nops)]
+    done_ev = [torch.cuda.Event() for _ in range(nops)]
+    out_ev = [torch.cuda.Event() for _ in range(nops)]
+
     def e2e_step():
-        for k in range(len(ops)):
-            for x, h in zip(staged[k], host_in[k]):
-                x.copy_(h, non_blocking=True)
+        for k in range(nops):
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(done_ev[k])
+                for x, h in zip(staged[k], host_in[k]):
+                    x.copy_(h, non_blocking=True)
+                staged_ev[k].record(s_in)
+            stream.wait_event(staged_ev[k])
+            stream.wait_event(out_ev[k])
             one(k)
-            host_out[k].copy_(outs[k], non_blocking=True)
+            done_ev[k].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done_ev[k])
+                host_out[k].copy_(outs[k], non_blocking=True)
+                out_ev[k].record(s_out)
+
+    def e2e_join():
+        stream.wait_stream(s_in)
+        stream.wait_stream(s_out)
 
     for _ in range(2):
         e2e_step()
+    e2e_join()
     torch.cuda.synchronize()
     dist.barrier()
     steps2 = max(3, min(args.steps, 10))
     ev0.record(stream)
+    s_in.wait_event(ev0)
     for _ in range(steps2):
         e2e_step()
+    e2e_join()
     ev1.record(stream)
     torch.cuda.synchronize()
     e2e = torch.tensor([ev0.elapsed_time(ev1) / steps2], device=dev)
@@ -309,6 +341,11 @@ def run_bench(args, rank: int, world: int, dev):
                                                           + ("gathered and stored into the readers' buffers over "
                                                              "NVLink by one kernel of this library, flag barriers "
                                                              "with bounded waits"
+                                                             + (", pushed peer by peer on a side stream while the "
+                                                                "edges of the owners that have landed are aggregated"
+                                                                if hp.streamed else "")
+                                                             + (", the epoch's launches replayed as one CUDA graph"
+                                                                if graphed else "")
                                                              + (", later chunks pushed on a side stream beside the "
                                                                 "aggregation" if getattr(args, "overlap", False) else "")
                                                              if hp.fabric is not None else
@@ -327,7 +364,8 @@ def run_bench(args, rank: int, world: int, dev):
             "clocks": clocks.summary(), "check": check,
             "e2e": {"value": round(e2e.item(), 4), "unit": "ms/epoch", "h2d_bytes_per_step": int(byts[0]),
                     "d2h_bytes_per_step": int(byts[1]),
-                    "what": "each rank stages its rows from pinned host memory, exchanges, aggregates, copies results back"},
+                    "what": "each rank stages its rows from pinned host memory, exchanges, aggregates, copies results "
+                            "back; copies in, kernels and copies out on three streams"},
             "gpu_launches": launches * args.steps, "cpu_baseline": None,
             "setup_s": round(setup_s, 2), "prep_s": round(hp.prep_s, 4),
         }

@@ -35,6 +35,7 @@ SIGNATURES = {
     "eppgcn_tile_plan_destroy": (None, [_P]),
     "eppgcn_tile_plan_info": (_I, [_P, _P]),
     "eppgcn_spmm_tiles": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
+    "eppgcn_spmm_tiles_add": (_I, [_P, _LL, _P, _LL, _P, _P, _I, _P]),
     "eppgcn_debug_status": (_I, [_P, _I]),
     "eppgcn_update_scaled": (_I, [_P, _LL, _P, _LL, _P, _LL, _P, _I, _I, _I, _I, _P]),
     "eppgcn_weight_grad": (_I, [_P, _P, _LL, _P, _LL, _I, _I, _I, _P]),
@@ -51,6 +52,10 @@ SIGNATURES = {
     "eppgcn_count_nonzero": (_I, [_P, _I, _P, _P]),
     "eppgcn_push_rows": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _LL, _P]),
     "eppgcn_peer_barrier": (_I, [_P, _I, _I, C.c_uint, _LL, _P, _P]),
+    "eppgcn_peer_barrier_counted": (_I, [_P, _I, _I, _P, _LL, _P, _P]),
+    "eppgcn_push_rows_signal": (_I, [_P, _LL, _P, _P, _P, _P, _LL, _I, _I, _I, _P, _P, _P, _P]),
+    "eppgcn_bump_counter": (_I, [_P, _P]),
+    "eppgcn_wait_landed": (_I, [_P, C.c_uint, _P, _LL, _P, _P]),
     "eppgcn_build_part_host": (_I, [_I, _P, _I, _P, _P, C.POINTER(_LL)]),
     "eppgcn_map_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
     "eppgcn_bucket_back_part_size": (_I, [_I, _I, C.POINTER(_I)]),
@@ -274,6 +279,16 @@ def spmm_tiles(src, plan, row_scale=None, out=None):
     return out
 
 
+def spmm_tiles_add(src, plan, row_scale, out):
+    """Adds ``row_scale[r] * sum_e src[col_idx[e]]`` over the rows of ``plan`` to ``out``."""
+    n = plan.info["rows"]
+    dim = src.size(1)
+    check(lib().eppgcn_spmm_tiles_add(
+        _out_rows(out, n, dim, "out"), _row_stride(out, "out"), src.data_ptr(), _row_stride(src, "src"), plan._handle,
+        None if row_scale is None else _dev(row_scale, torch.float32, "row_scale"), dim, _stream()))
+    return out
+
+
 def mask_forward(ids, part_ptr, edge_list, src_mask, ngh_mask, back_edge_mask, node_degs,
                  num_layers, layer, blockx=4, blocky=16, row_offset=0):
     is_last = int(layer == num_layers)
@@ -376,6 +391,37 @@ def push_rows(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, dim=
                                  sp, pb, fr, int(peer_ld), int(dim), world, int(start_row), _stream()))
 
 
+def push_rows_signal(rows, send_idx, send_ptr, peer_base, peer_first_row, peer_ld, rank, peer_landed, epoch, done,
+                     dim=None):
+    """:func:`push_rows` served peer by peer, each peer's word ``rank`` of its "landed" array
+    (``peer_landed``: addresses as mapped into this process) set to ``epoch[0]`` once its rows are
+    stored; ``epoch`` and ``done`` (16 zeroed words of scratch) are int32 device tensors."""
+    world = len(peer_base)
+    dim = rows.size(1) if dim is None else dim
+    sp = (_LL * (world + 1))(*[int(v) for v in send_ptr])
+    pb = (_P * world)(*[int(v) if v else None for v in peer_base])
+    fr = (_LL * world)(*[int(v) for v in peer_first_row])
+    pl = (_P * world)(*[int(v) if v else None for v in peer_landed])
+    check(lib().eppgcn_push_rows_signal(rows.data_ptr(), _row_stride(rows, "rows"), _dev(send_idx, torch.int32, "send_idx"),
+                                        sp, pb, fr, int(peer_ld), int(dim), world, int(rank), pl,
+                                        _dev(epoch, torch.int32, "epoch"), _dev(done, torch.int32, "done"), _stream()))
+
+
+def bump_counter(counter):
+    """Adds one to an int32 device word, in stream order."""
+    check(lib().eppgcn_bump_counter(_dev(counter, torch.int32, "counter"), _stream()))
+
+
+def wait_landed(landed, owners, epoch, status, max_polls=4_000_000):
+    """Makes the stream wait (bounded) until ``landed[r] >= epoch[0]`` for every rank ``r`` in ``owners``;
+    int32 device tensors, see ``eppgcn_wait_landed``."""
+    mask = 0
+    for r in owners:
+        mask |= 1 << int(r)
+    check(lib().eppgcn_wait_landed(_dev(landed, torch.int32, "landed"), mask, _dev(epoch, torch.int32, "epoch"),
+                                   int(max_polls), _dev(status, torch.int32, "status"), _stream()))
+
+
 def peer_barrier(peer_flags, rank, value, status, max_polls=4_000_000):
     """Enqueues barrier number ``value`` over the ranks whose flag arrays
     (addresses as mapped into this process) are ``peer_flags``; ``status`` is a
@@ -384,6 +430,15 @@ def peer_barrier(peer_flags, rank, value, status, max_polls=4_000_000):
     pf = (_P * world)(*[int(v) for v in peer_flags])
     check(lib().eppgcn_peer_barrier(pf, int(rank), world, int(value) & 0xffffffff, int(max_polls),
                                     _dev(status, torch.int32, "status"), _stream()))
+
+
+def peer_barrier_counted(peer_flags, rank, counter, status, max_polls=4_000_000):
+    """Enqueues the next barrier of the sequence ``counter`` (a device int32 word, zero before the
+    first barrier) numbers; see :func:`peer_barrier`.  Can be captured into a CUDA graph."""
+    world = len(peer_flags)
+    pf = (_P * world)(*[int(v) for v in peer_flags])
+    check(lib().eppgcn_peer_barrier_counted(pf, int(rank), world, _dev(counter, torch.int32, "counter"), int(max_polls),
+                                            _dev(status, torch.int32, "status"), _stream()))
 
 
 def count_nonzero(values) -> int:

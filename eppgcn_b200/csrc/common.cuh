@@ -48,6 +48,16 @@ constexpr unsigned kFull = 0xffffffffu;
 
 __host__ __device__ inline long long ceil_div_ll(long long a, long long b) { return (a + b - 1) / b; }
 
+// Flag words another GPU writes or reads: release / acquire at system scope.
+__device__ __forceinline__ void store_release_sys(unsigned *p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned load_acquire_sys(const unsigned *p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 // ---------------------------------------------------------------------------
 // Tile descriptor of the chained (decoupled look-back) scans.
 // One 64-bit word per tile: bits 63..62 state, 61..31 field B, 30..0 field A.

@@ -96,6 +96,7 @@ struct TileArgs {
   int dim;                        // columns handled by this launch
   int lanes;                      // lanes per row, ceil(dim / 4)
   int num_rows, num_sources;      // limits of the ids (looked at by the bounds-checking build only)
+  int accumulate;                 // 1: every row is added to what `out` holds (red.global.add) instead of stored
   ClassTable t;
 };
 
@@ -138,7 +139,7 @@ __device__ __forceinline__ void put_row(const TileArgs &a, float *out_lane, int 
   const float s = a.row_scale ? __ldg(a.row_scale + row) : 1.f;
   const float val[4] = {acc[0] * s, acc[1] * s, acc[2] * s, acc[3] * s};
   float *dst = out_lane + static_cast<long long>(row) * a.out_ld;
-  if (rid < 0) add_row<4>(dst, val, n, OV);
+  if (rid < 0 || a.accumulate) add_row<4>(dst, val, n, OV);
   else store_row<4>(dst, val, n, OV);
 }
 
@@ -243,7 +244,7 @@ __global__ void __launch_bounds__(kTileThreads, kTileMinBlocks) tiled_spmm_kerne
       if (rid != -1 && has_cols) {
         const float val[4] = {acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale};
         float *dst = out_lane + static_cast<long long>(row) * a.out_ld;
-        if (rid < 0) add_row<4>(dst, val, n, OV);
+        if (rid < 0 || a.accumulate) add_row<4>(dst, val, n, OV);
         else store_row<4>(dst, val, n, OV);
       }
     } else {
@@ -672,6 +673,26 @@ EPP_EXPORT int eppgcn_tile_plan_active_rows(const eppgcn_tile_plan *plan, const 
   return EPP_OK;
 }
 
+// The tile launches of one aggregation (one unless the row is wider than 128 columns).
+static int run_tiles(float *out, long long out_ld, const float *src, long long src_ld, const eppgcn_tile_plan *plan,
+                     const float *row_scale, int dim, int ovec, int accumulate, cudaStream_t s) {
+  if (plan->num_ranks == 0) return EPP_OK;
+  EPP_REQUIRE(src, "null pointer");
+  EPP_REQUIRE(src_ld % 4 == 0 && src_ld >= (dim + 3) / 4 * 4 && src_ld <= 0x3fffffffLL && aligned(src, 16),
+              "source rows must be 16-byte aligned and padded to a multiple of 4 floats");
+  for (int col0 = 0; col0 < dim; col0 += 128) {
+    TileArgs a{};
+    a.out = out + col0; a.out_ld = out_ld; a.src = src + col0; a.src_ld = src_ld;
+    a.slots = plan->slots; a.row_of = plan->row_of; a.row_scale = row_scale;
+    a.dim = dim - col0 < 128 ? dim - col0 : 128; a.lanes = lanes_for_dim(a.dim); a.t = plan->table;
+    a.num_rows = plan->num_rows; a.num_sources = plan->num_sources;
+    a.accumulate = accumulate;
+    const int rc = ovec == 4 ? launch_tiles<4>(a, s) : ovec == 2 ? launch_tiles<2>(a, s) : launch_tiles<1>(a, s);
+    if (rc != EPP_OK) return rc;
+  }
+  return EPP_OK;
+}
+
 EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src, long long src_ld,
                                  const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -700,20 +721,22 @@ EPP_EXPORT int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src,
     else zero_listed_rows_kernel<1><<<g, 256, 0, s>>>(out, out_ld, dim, plan->zero_rows, plan->num_zero);
     EPP_CHECK_LAUNCH("zero_listed_rows_kernel");
   }
-  if (plan->num_ranks == 0) return EPP_OK;
-  EPP_REQUIRE(src, "null pointer");
-  EPP_REQUIRE(src_ld % 4 == 0 && src_ld >= (dim + 3) / 4 * 4 && src_ld <= 0x3fffffffLL && aligned(src, 16),
-              "source rows must be 16-byte aligned and padded to a multiple of 4 floats");
-  for (int col0 = 0; col0 < dim; col0 += 128) {          // one launch unless the row is wider than 128
-    TileArgs a{};
-    a.out = out + col0; a.out_ld = out_ld; a.src = src + col0; a.src_ld = src_ld;
-    a.slots = plan->slots; a.row_of = plan->row_of; a.row_scale = row_scale;
-    a.dim = dim - col0 < 128 ? dim - col0 : 128; a.lanes = lanes_for_dim(a.dim); a.t = plan->table;
-    a.num_rows = plan->num_rows; a.num_sources = plan->num_sources;
-    const int rc = ovec == 4 ? launch_tiles<4>(a, s) : ovec == 2 ? launch_tiles<2>(a, s) : launch_tiles<1>(a, s);
-    if (rc != EPP_OK) return rc;
-  }
-  return EPP_OK;
+  return run_tiles(out, out_ld, src, src_ld, plan, row_scale, dim, ovec, 0, s);
+}
+
+EPP_EXPORT int eppgcn_spmm_tiles_add(float *out, long long out_ld, const float *src, long long src_ld,
+                                     const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  EPP_REQUIRE(plan, "null plan");
+  EPP_REQUIRE(dim >= 1, "dim < 1");
+  EPP_REQUIRE(out_ld == 0 || out_ld >= dim, "out_ld must be 0 or >= dim");
+  if (plan->num_rows == 0) return EPP_OK;
+  EPP_REQUIRE(out, "null pointer");
+  if (out_ld == 0) out_ld = dim;
+  int ovec = 1;
+  if (out_ld % 4 == 0 && aligned(out, 16)) ovec = 4;
+  else if (out_ld % 2 == 0 && aligned(out, 8)) ovec = 2;
+  return run_tiles(out, out_ld, src, src_ld, plan, row_scale, dim, ovec, 1, s);
 }
 
 EPP_EXPORT int eppgcn_debug_status(int *out4, int reset) {

@@ -42,6 +42,7 @@ from __future__ import annotations
 
 import json
 import os
+import contextlib
 import time
 from dataclasses import dataclass
 
@@ -302,7 +303,18 @@ class PeerFabric:
         flags, self.flag_ptrs = self.alloc((64,), torch.int32)
         flags.zero_()
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        # Barriers are numbered by a word on the device (every launch takes the next number), so that a captured
+        # sequence of launches can be replayed; ``count`` is the host's tally of the barriers it has enqueued.
+        self.counter = torch.zeros(1, dtype=torch.int32, device=dev)
         self.count, self.max_polls = 0, max_polls    # a poll takes about a microsecond: ranks may be ~10 s apart
+        # The streamed exchange: word r of ``landed`` is stored by rank r when its rows of the current exchange
+        # have arrived here; ``epoch`` numbers the exchanges (advanced on the device, in stream order);
+        # ``done`` is the push kernel's scratch; pushes run on ``comm`` beside the aggregation.
+        self.landed, self.landed_ptrs = self.alloc((64,), torch.int32)
+        self.landed.zero_()
+        self.epoch = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done = torch.zeros(16, dtype=torch.int32, device=dev)
+        self.comm = torch.cuda.Stream(device=dev, priority=-1)     # its blocks are placed before the aggregation's
         _sync(dev)
         dist.barrier(self.group)                     # every rank's flag words are zero before the first barrier
 
@@ -321,7 +333,22 @@ class PeerFabric:
 
     def barrier(self):
         self.count += 1
-        self.capi.peer_barrier(self.flag_ptrs, self.rank, self.count, self.status, self.max_polls)
+        self.capi.peer_barrier_counted(self.flag_ptrs, self.rank, self.counter, self.status, self.max_polls)
+
+    @contextlib.contextmanager
+    def side_stream(self):
+        """Work enqueued inside runs on the fabric's side stream, after everything the current stream holds
+        so far; :meth:`join_side_stream` makes the current stream wait for it."""
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        with torch.cuda.stream(self.comm):
+            self.comm.wait_event(ready)
+            yield
+            self._side_done = torch.cuda.Event()
+            self._side_done.record(self.comm)
+
+    def join_side_stream(self):
+        torch.cuda.current_stream().wait_event(self._side_done)
 
     def check(self):
         code = int(self.status.item())
@@ -373,6 +400,7 @@ class DealtHalo:
         self.remap = remap.to(torch.int32)
         b = torch.arange(world + 1, device=dev, dtype=torch.int64) * n_loc
         cut = torch.searchsorted(self.needed, b)
+        self.cut = cut                                 # buffer rows [cut[o], cut[o+1]) come from rank o
         counts_in = cut[1:] - cut[:-1]
         self.recv_counts = counts_in.tolist()
         request = self.needed % n_loc                                      # row ids local to their owner
@@ -507,6 +535,38 @@ class DealtHalo:
         return out
 
 
+    def needs_barrier(self, key) -> bool:
+        """Whether an exchange into the buffers ``key`` must first wait for their readers: only when no
+        barrier has been enqueued since they were last aggregated from (see :meth:`start`)."""
+        stamp = self._stamps.get(key)
+        return self.lead_barrier or stamp is None or self.fabric.count <= stamp
+
+    def start_streamed(self, local, buf, peers, scale=None):
+        """The streamed form of the peer-store exchange of one buffer: the rows are pushed peer by peer on
+        the fabric's side stream, every peer being told as soon as its rows are complete, while the caller
+        aggregates on the current stream (first the edges whose sources it owns, then owner by owner,
+        each launch behind a wait for that owner's word), and calls :meth:`end_streamed` after its last
+        aggregation launch."""
+        fab = self.fabric
+        key = (buf.size(1), "streamed", buf.data_ptr())
+        fab.capi.bump_counter(fab.epoch)
+        if self.needs_barrier(key):
+            fab.barrier()
+        if local is not None:
+            self._place_own(buf, local, scale)
+        with fab.side_stream():
+            wide = _padded_rows(buf[self.num_remote:])
+            fab.capi.push_rows_signal(wide, self.send_idx32, self.send_ptr, peers, self.peer_first_row, wide.size(1),
+                                      self.rank, fab.landed_ptrs, fab.epoch, fab.done)
+        self._last_key = key
+
+    def end_streamed(self):
+        """After the caller's last aggregation launch of a streamed exchange: the current stream waits for
+        the end of this rank's push, and the buffer counts as read up to here."""
+        self.fabric.join_side_stream()
+        self._stamps[self._last_key] = self.fabric.count
+
+
 class MaskedGather:
     """Exchange of the rows selected by a vertex mask that every rank holds
     (the source mask of a backward layer: only those rows of ``d_output`` are
@@ -564,11 +624,12 @@ class DistHotPath:
     """
 
     def __init__(self, ds, dev, rank: int, world: int, back_size: int = 32, group=None,
-                 exchange: str = "balanced", chunks: int = 1, transport: str = "push", overlap: bool = False):
+                 exchange: str = "balanced", chunks: int = 1, transport: str = "push", overlap: bool = False,
+                 streamed: bool = False, owner_groups: int = 0):
         import eppgcn_b200
         from eppgcn_b200 import capi
         self.capi, self.dev, self.rank, self.world, self.group = capi, dev, rank, world, group
-        self.mode, self.chunks, self.fabric = exchange, chunks, None
+        self.mode, self.chunks, self.fabric, self.streamed = exchange, chunks, None, False
         gnna = eppgcn_b200.load_gnnadvisor()
         on_device = torch.is_tensor(getattr(ds, "indptr", None))      # DeviceWorkload: the graph never touches the host
         relabel = exchange in ("balanced", "balanced_halo")
@@ -682,6 +743,9 @@ class DistHotPath:
                         print("eppgcn_b200.dist: peer-store transport unavailable, using NCCL all-to-all"
                               + (f" ({why[:200]})" if why else ""), file=sys.stderr, flush=True)
                     self.fabric = None
+            # streamed: push and aggregation overlap owner by owner (peer-store transport, no chunk overlap)
+            self.streamed = streamed and self.fabric is not None and not overlap
+            self.owner_groups = owner_groups if owner_groups > 0 else world
             self.fwd_plan = DealtHalo(self.col, n_loc, rank, world, group, self.fabric)
             self.fwd_plan.overlap = overlap
             self.col_c = self.fwd_plan.remap
@@ -752,6 +816,75 @@ class DistHotPath:
                                                  self.back_size, out=out, deg_row=self.deg_row,
                                                  num_rows=self.shard.num_rows)
 
+    def _segment_plans(self, kind, i):
+        """The edge list of one aggregation cut by the owner of the source row into tile plans:
+        ``[(owners, plan)]``, first the edges whose sources this rank owns (``owners = ()``), then the other
+        ranks in the order their rows arrive (rank+1, rank+2, ...), bundled into at most
+        ``self.owner_groups`` groups of consecutive owners.  Sources are positions in the exchange buffer;
+        a plan is ``None`` when the rank's own part has no edge."""
+        cache = self.__dict__.setdefault("_seg_plans", {})
+        i = 0 if kind == "fwd" else i                   # every forward layer aggregates over the same edge list
+        if (kind, i) in cache:
+            return cache[(kind, i)]
+        dev, n_loc, w = self.dev, self.n_loc, self.world
+        if kind == "fwd":
+            plan = self.fwd_plan
+            pos = self.col_c.long()
+            counts = (self.row[1:] - self.row[:-1]).long()
+            rows = torch.repeat_interleave(torch.arange(n_loc, device=dev), counts)
+        else:
+            p = self.path[i]
+            plan = p["plan"]
+            pos = p["edges_c"][:p["valid"]].long()
+            rows = p["id"][:p["valid"]].long()
+        # positions from cut[o] up to cut[o+1] belong to owner o; the rank's own rows follow all of them
+        owner = torch.bucketize(pos, plan.cut[1:].contiguous(), right=True)
+        arriving = [(self.rank + k) % w for k in range(1, w) if plan.recv_counts[(self.rank + k) % w] > 0]
+        groups = max(1, min(self.owner_groups, len(arriving))) if arriving else 0
+        bundles = [()] + [tuple(arriving[g * len(arriving) // groups:(g + 1) * len(arriving) // groups])
+                          for g in range(groups)]
+        out = []
+        for owners in bundles:
+            pick = owner == w if not owners else torch.isin(owner, torch.tensor(owners, device=dev))
+            count = int(pick.sum().item())
+            tp = None
+            if count:
+                tp = self.capi.TilePlan.from_ids(rows[pick].to(torch.int32), pos[pick].to(torch.int32), count, n_loc,
+                                                 num_sources=plan.num_rows)
+            if owners and tp is None:
+                continue
+            out.append((owners, tp))
+        cache[(kind, i)] = out
+        return out
+
+    def _segments_spmm(self, kind, i, buf, out, wait: bool):
+        """The aggregation of one buffer, bundle by bundle: the rank's own sources are stored, the others
+        added; with ``wait`` the stream first waits for the rows of a bundle's owners (streamed exchange)."""
+        fab = self.fabric
+        for owners, tp in self._segment_plans(kind, i):
+            if not owners:
+                if tp is None:
+                    out.zero_()
+                else:
+                    self.capi.spmm_tiles(buf, tp, self.deg_row, out=out)
+                continue
+            if wait:
+                fab.capi.wait_landed(fab.landed, owners, fab.epoch, fab.status, fab.max_polls)
+            self.capi.spmm_tiles_add(buf, tp, self.deg_row, out)
+
+    def _streamed_op(self, kind, i, local, out_local, plan, bufs):
+        """Exchange and aggregation overlapped owner by owner (see :meth:`DealtHalo.start_streamed`), chunk
+        after chunk.  Backward rows are multiplied by their source-side factor while they are placed."""
+        if kind == "bwd":
+            self.path[i].setdefault("prescaled", {})[bufs[0][1].size(1)] = True
+        dc = out_local.size(1) // len(bufs)
+        for c, (peers, buf) in enumerate(bufs):
+            rows = None if local is None else local[:, c * dc:(c + 1) * dc]
+            plan.start_streamed(rows, buf, peers, self.deg_row if kind == "bwd" else None)
+            self._segments_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc], wait=True)
+            plan.end_streamed()
+        return out_local
+
     def _dealt_op(self, kind, i, local, out_local):
         """Chunked exchange + aggregation: chunk ``c`` is aggregated (straight into
         its column block of ``out_local``) while chunk ``c + 1`` travels.  A backward
@@ -762,6 +895,10 @@ class DistHotPath:
         applies the factor per edge."""
         plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
         scale = None
+        if self.streamed and (kind == "fwd" or local is not None):
+            bufs = plan.buffers(out_local.size(1), self.chunks)
+            if all(self._tiles_can_read(b) for _, b in bufs):
+                return self._streamed_op(kind, i, local, out_local, plan, bufs)
         if kind == "bwd":
             d = out_local.size(1)
             bufs = plan.buffers(d, self.chunks)
@@ -779,6 +916,31 @@ class DistHotPath:
                 work.wait()
             self._halo_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc])
         return out_local
+
+    def graphed(self, fn, warmup: int = 2):
+        """Captures the launches of ``fn()`` (aggregations of this object on fixed tensors) into a CUDA
+        graph and returns a callable that replays them: one submission per step instead of a dozen, which
+        keeps the ranks in step with one another between the flag barriers.  Only this library's kernels
+        and peer stores are captured; with a transport that calls NCCL, or on the CPU, ``fn`` itself is
+        returned.  ``fn`` must be the steady state: it runs ``warmup`` times first (plans are built and the
+        exchange's barrier bookkeeping settles), every rank must capture and replay the same sequence,
+        and between replays no other aggregation of this object may run."""
+        dev = torch.device(self.dev)
+        if dev.type != "cuda" or (self.world > 1 and self.fabric is None):
+            return fn
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 1)):
+                fn()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        _sync(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            fn()
+        _sync(dev)
+        self.__dict__.setdefault("_graphs", []).append(graph)
+        return graph.replay
 
     def halo_inputs(self, kind, i, d):
         """Where the producer of an aggregation's input puts this rank's rows (see
@@ -800,8 +962,13 @@ class DistHotPath:
         plan = self.fwd_plan if kind == "fwd" else self.path[i]["plan"]
         bufs = plan.buffers(out_local.size(1), self.chunks)
         dc = out_local.size(1) // len(bufs)
+        streamed = self.streamed and all(self._tiles_can_read(b) for _, b in bufs) and \
+            (kind == "fwd" or self.path[i].get("prescaled", {}).get(bufs[0][1].size(1)))
         for c, (_, buf) in enumerate(bufs):
-            self._halo_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc])
+            if streamed:
+                self._segments_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc], wait=False)
+            else:
+                self._halo_spmm(kind, i, buf, out_local[:, c * dc:(c + 1) * dc])
 
     def forward_halo(self, local, out_local):
         """Exchange of the referenced (pre-scaled) source rows, then the local forward aggregation."""

@@ -138,6 +138,12 @@ int eppgcn_spmm_backward_compacted(float *d_in, long long d_in_ld, const float *
  *           multiple of 4 floats, base 16-byte aligned.
  * row_scale destination-side factor per row id, or NULL for 1.
  *
+ * eppgcn_spmm_tiles_add adds the same sums to what `out` already holds
+ * (red.global.add per row, nothing is cleared): an aggregation whose edge list
+ * is cut into several plans runs the first with eppgcn_spmm_tiles and the others
+ * with this entry point, one after the other on a stream.  No counterpart in
+ * the reference.
+ *
  * eppgcn_pack_scaled_rows prepares the source of a backward aggregation, in
  * place of the per-edge degrees[...] factor of ours_backward_cuda_kernel
  * (EPPGCN_kernel.cu:660-663):  dst[r][0..dim) = scale[r] * x[r][0..dim)  into
@@ -159,6 +165,8 @@ int eppgcn_tile_plan_info(const eppgcn_tile_plan *plan, long long *out8);
 int eppgcn_tile_plan_active_rows(const eppgcn_tile_plan *plan, const int **rows_dev, int *count);
 int eppgcn_spmm_tiles(float *out, long long out_ld, const float *src, long long src_ld,
                       const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream);
+int eppgcn_spmm_tiles_add(float *out, long long out_ld, const float *src, long long src_ld,
+                          const eppgcn_tile_plan *plan, const float *row_scale, int dim, void *stream);
 int eppgcn_pack_scaled_rows(float *dst, long long dst_ld, const float *x, long long ldx,
                             const float *scale, const eppgcn_tile_plan *plan, int num_rows, int dim,
                             void *stream);
@@ -346,7 +354,7 @@ int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *st
 
 /* ------------------------------------------------------------------------
  * Row exchange between the GPUs of one node.  No counterpart in the
- * reference, which is single-GPU: these two entry points serve the
+ * reference, which is single-GPU: these entry points serve the
  * row-partitioned aggregation, where a rank's edges reference rows that
  * other ranks own.
  *
@@ -382,6 +390,35 @@ int eppgcn_count_nonzero(const int *values, int length, int *count_dev, void *st
  * beforehand) and returns; the context stays usable.  While *status_dev is
  * non-zero, later barriers announce their arrival but do not wait, so a
  * broken group drains quickly; the caller reads the word and gives up.
+ *
+ * eppgcn_push_rows_signal is eppgcn_push_rows served peer by peer (rank-1,
+ * rank-2, ... modulo world, so that every rank receives its right-hand
+ * neighbour's rows first and no two ranks store into one peer at a time) with
+ * a signal per peer: once all rows for peer r are stored, word `rank` of
+ * peer_landed[r] (HOST array of every rank's `world`-word "landed" array as
+ * mapped into this process, zero at the start) is set to *epoch_dev (release,
+ * system scope).  Peers that get no rows are not signalled.  epoch_dev is a
+ * device word the caller advances before every exchange (eppgcn_bump_counter,
+ * on a stream that orders it before this launch and before the readers'
+ * eppgcn_wait_landed launches); done_dev is scratch of
+ * 16 zeroed device words that the kernel leaves zeroed.  A rank sends nothing
+ * to itself: send_ptr[rank] == send_ptr[rank + 1].
+ *
+ * eppgcn_bump_counter adds one to a device word, in stream order.
+ *
+ * eppgcn_wait_landed makes the stream wait until word r of landed_dev (this
+ * rank's own "landed" array) has reached *epoch_dev for every rank r whose bit
+ * is set in `owners` (counters that only grow, compared modulo 2^32).  One warp
+ * polls; the wait is bounded like the barrier's: after max_polls polls
+ * EPP_ERR_PEER_TIMEOUT is stored to *status_dev, and while that word is
+ * non-zero later waits return at once.
+ *
+ * eppgcn_peer_barrier_counted is the same barrier numbered on the device:
+ * every launch takes the next number from *counter_dev (a 32-bit word of this
+ * rank's memory, zero before the first barrier, touched by nothing else), so
+ * a launch captured into a CUDA graph can be replayed.  All ranks must run the
+ * same sequence of barriers on one flag array, and must not mix the two
+ * numberings on it.
  */
 int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
                      const long long *send_ptr, void *const *peer_base,
@@ -389,6 +426,16 @@ int eppgcn_push_rows(const float *rows, long long rows_ld, const int *send_idx,
                      long long start_row, void *stream);
 int eppgcn_peer_barrier(void *const *peer_flags, int rank, int world, unsigned value,
                         long long max_polls, int *status_dev, void *stream);
+int eppgcn_peer_barrier_counted(void *const *peer_flags, int rank, int world, unsigned *counter_dev,
+                                long long max_polls, int *status_dev, void *stream);
+int eppgcn_push_rows_signal(const float *rows, long long rows_ld, const int *send_idx,
+                            const long long *send_ptr, void *const *peer_base,
+                            const long long *peer_first_row, long long peer_ld, int dim, int world,
+                            int rank, void *const *peer_landed, const unsigned *epoch_dev,
+                            unsigned *done_dev, void *stream);
+int eppgcn_bump_counter(unsigned *counter_dev, void *stream);
+int eppgcn_wait_landed(const unsigned *landed_dev, unsigned owners, const unsigned *epoch_dev,
+                       long long max_polls, int *status_dev, void *stream);
 
 /* ------------------------------------------------------------------------
  * Host-side helpers (CPU pointers, synchronous).

@@ -7,6 +7,8 @@ reduction, compaction and splitting per shard, the exchange plans of every mode
 (re-indexed edge lists, degree vectors in buffer order, column chunks) and the
 collectives.  Each rank's results are checked against the float64 oracle of the
 whole graph.  The kernels themselves are checked on GPUs elsewhere."""
+import contextlib
+
 import numpy as np
 import pytest
 import torch
@@ -93,6 +95,14 @@ def _install_oracle_double():
         out.copy_(torch.from_numpy(acc.astype(np.float32)))
         return out
 
+    def spmm_tiles_add(src, plan, row_scale, out):
+        acc = np.zeros((plan.num_rows, src.size(1)))
+        np.add.at(acc, plan.rows, src.numpy().astype(np.float64)[plan.cols])
+        if row_scale is not None:
+            acc *= row_scale.numpy().astype(np.float64)[:plan.num_rows, None]
+        out.add_(torch.from_numpy(acc.astype(np.float32)))
+        return out
+
     def pack_scaled_rows(x, scale, plan=None, out=None, pad_to=8):
         assert plan is None
         out.copy_(x * scale[:, None])
@@ -100,7 +110,8 @@ def _install_oracle_double():
 
     for name, fn in dict(mask_forward=mask_forward, compact_mask=compact_mask, split_parts=split_parts,
                          spmm_forward=spmm_forward, spmm_backward_compacted=spmm_backward_compacted,
-                         spmm_tiles=spmm_tiles, TilePlan=TilePlan, pack_scaled_rows=pack_scaled_rows).items():
+                         spmm_tiles=spmm_tiles, spmm_tiles_add=spmm_tiles_add, TilePlan=TilePlan,
+                         pack_scaled_rows=pack_scaled_rows).items():
         setattr(capi, name, fn)
 
 
@@ -108,8 +119,9 @@ class SharedFileFabric:
     """Stand-in for ``PeerFabric`` on CPU ranks of one machine: a buffer is a
     file in shared memory that every rank maps, "peer addresses" are the mapped
     tensors themselves, the push is an indexed copy into them and the barrier is
-    the process group's.  Same three members as the real one (``alloc``,
-    ``barrier``, ``capi.push_rows``), so the plans run unchanged."""
+    the process group's.  For the streamed exchange the "landed" words are one more shared file, the
+    signalling push writes them after its rows, and the wait polls them.  Same members as the real
+    one, so the plans run unchanged."""
 
     tag = "0"
 
@@ -117,18 +129,36 @@ class SharedFileFabric:
         import types
         self.rank, self.world, self.group = rank, world, group
         self.count, self.files, self.keep = 0, [], []
-        self.capi = types.SimpleNamespace(push_rows=self.push_rows)
+        self.capi = types.SimpleNamespace(push_rows=self.push_rows, push_rows_signal=self.push_rows_signal,
+                                          bump_counter=self.bump_counter, wait_landed=self.wait_landed)
+        self._landed = None                            # allocated at first use: the constructor has no collective
+        self.epoch = torch.zeros(1, dtype=torch.int32)
+        self.done = torch.zeros(16, dtype=torch.int32)
+        self.status = torch.zeros(1, dtype=torch.int32)
+        self.max_polls = 20_000
+        self.signals = 0
 
     @staticmethod
     def available(dev, group=None):
         return True
 
+    @property
+    def landed(self):
+        if self._landed is None:
+            self._landed = self.alloc((64,), torch.int32)
+        return self._landed[0]
+
+    @property
+    def landed_ptrs(self):
+        self.landed
+        return self._landed[1]
+
     def alloc(self, shape, dtype=torch.float32):
         import os
-        assert dtype == torch.float32
+        np_dtype = {torch.float32: np.float32, torch.int32: np.int32}[dtype]
         index = len(self.files)
         names = [f"/dev/shm/eppgcn_test_{self.tag}_{index}_{r}" for r in range(self.world)]
-        own = np.lib.format.open_memmap(names[self.rank], mode="w+", dtype=np.float32, shape=tuple(shape))
+        own = np.lib.format.open_memmap(names[self.rank], mode="w+", dtype=np_dtype, shape=tuple(shape))
         own[...] = 0
         own.flush()
         dist.barrier(self.group)
@@ -146,6 +176,36 @@ class SharedFileFabric:
             lo, hi = send_ptr[r], send_ptr[r + 1]
             if hi > lo:
                 peer[first_row[r]:first_row[r] + hi - lo, :dim] = rows[send_idx[lo:hi].long()]
+
+    def push_rows_signal(self, rows, send_idx, send_ptr, peers, first_row, dim, rank, landed, epoch, done):
+        assert rank == self.rank and send_ptr[rank] == send_ptr[rank + 1]
+        for k in range(1, self.world):                 # served leftwards from the rank, like the kernel
+            r = (rank - k) % self.world
+            lo, hi = send_ptr[r], send_ptr[r + 1]
+            if hi > lo:
+                peers[r][first_row[r]:first_row[r] + hi - lo, :dim] = rows[send_idx[lo:hi].long()]
+                landed[r][rank] = int(epoch[0])
+                self.signals += 1
+
+    @staticmethod
+    def bump_counter(counter):
+        counter += 1
+
+    def wait_landed(self, landed, owners, epoch, status, max_polls):
+        import time
+        for r in owners:
+            polls = 0
+            while int(landed[r]) - int(epoch[0]) < 0:
+                polls += 1
+                assert polls < max_polls, "the rows of another rank never arrived"
+                time.sleep(0.001)
+
+    @contextlib.contextmanager
+    def side_stream(self):
+        yield
+
+    def join_side_stream(self):
+        pass
 
     def barrier(self):
         self.count += 1
@@ -177,7 +237,9 @@ def _worker(rank, world, port, mode, results):
         ds = graphs.load_workload("cora", 0, layers=3)
         g, n = ds.graph, ds.num_nodes
         deg, train = ds.degrees.numpy().copy(), ds.train_mask.numpy().copy()
-        hp = D.DistHotPath(ds, torch.device("cpu"), rank, world, back_size=4, exchange=mode, chunks=chunks)
+        streamed = parts[3:4] == ["streamed"]
+        hp = D.DistHotPath(ds, torch.device("cpu"), rank, world, back_size=4, exchange=mode, chunks=chunks,
+                           streamed=streamed, owner_groups=int((parts[4:5] or ["0"])[0]))
         sh = hp.shard
         if hp.new_of_old is not None:
             old_of_new = np.full(hp.n, -1, dtype=np.int64)
@@ -223,6 +285,7 @@ def _worker(rank, world, port, mode, results):
                                                             conv["numParts"]))
         if parts[2:3] == ["push"]:
             ok &= isinstance(hp.fabric, SharedFileFabric) and hp.fabric.count > 0
+            ok &= hp.fabric.signals > 0 if streamed else hp.fabric.signals == 0
         if parts[2:3] == ["broken"]:
             ok &= hp.fabric is None
         results[rank] = bool(ok)
@@ -232,7 +295,9 @@ def _worker(rank, world, port, mode, results):
 
 @pytest.mark.timeout(600)
 @pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2",
-                                  "balanced_halo:1:push", "balanced_halo:2:push", "balanced_halo:1:broken"])
+                                  "balanced_halo:1:push", "balanced_halo:2:push", "balanced_halo:1:push:streamed",
+                                  "balanced_halo:2:push:streamed",
+                                  "balanced_halo:1:broken"])
 def test_two_gloo_ranks_match_the_whole_graph_oracle(mode):
     world = 2
     mgr = mp.get_context("spawn").Manager()
@@ -249,3 +314,13 @@ def test_three_ranks_and_a_vertex_count_that_does_not_divide(tmp_path):
     results = mgr.dict()
     mp.spawn(_worker, args=(world, free_port(), "balanced_halo:2:push", results), nprocs=world, join=True)
     assert dict(results) == {0: True, 1: True, 2: True}
+
+
+@pytest.mark.timeout(600)
+def test_four_ranks_with_the_owners_bundled_into_two_groups():
+    """The streamed exchange with more owners than groups: three arriving owners in two bundles."""
+    world = 4
+    mgr = mp.get_context("spawn").Manager()
+    results = mgr.dict()
+    mp.spawn(_worker, args=(world, free_port(), "balanced_halo:1:push:streamed:2", results), nprocs=world, join=True)
+    assert dict(results) == {r: True for r in range(world)}

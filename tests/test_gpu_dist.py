@@ -33,9 +33,12 @@ def _worker(rank, world, port, mode, results):
         g, n = ds.graph, ds.num_nodes
         deg = ds.degrees.numpy().copy()
         train = ds.train_mask.numpy().copy()
-        parts = mode.split(":")                                        # "balanced_halo:2:nccl"
+        parts = mode.split(":")                                        # "balanced_halo:2:nccl[:graph|overlap]"
         mode, chunks, transport = parts[0], (parts[1:2] or ["1"])[0], (parts[2:3] or ["push"])[0]
-        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange=mode, chunks=int(chunks), transport=transport)
+        extra = (parts[3:4] or [""])[0]
+        hp = D.DistHotPath(ds, dev, rank, world, back_size=8, exchange=mode, chunks=int(chunks), transport=transport,
+                           overlap=extra == "overlap", streamed="stream" in extra)
+        graph = "graph" in extra
         sh = hp.shard
         rng = np.random.Generator(np.random.PCG64(11))
         mats = [rng.standard_normal((n, d)).astype(np.float32) for d in (16, 22)]
@@ -82,6 +85,34 @@ def _worker(rank, world, port, mode, results):
                                                conv["numParts"])
                 err = np.abs(d_in.cpu().numpy()[have] - wb[mine[have]]) - (2e-6 + 2e-5 * np.abs(wb[mine[have]]))
                 ok &= bool(err.max() <= 0)
+        if graph:
+            # one forward and one compacted backward aggregation captured into a CUDA graph and replayed on new
+            # inputs: the barriers number themselves on the device, so every replay lines the ranks up again
+            d = 16
+            x_in = torch.zeros(sh.num_rows, d, device=dev)
+            b_in = torch.zeros(sh.num_rows, d, device=dev)
+            f_out = torch.empty(sh.num_rows, d, device=dev)
+            b_out = torch.empty(sh.num_rows, d, device=dev)
+
+            def step():
+                hp.forward_halo(x_in, f_out)
+                hp.backward_halo(0, b_in, b_out)
+
+            run = hp.graphed(step)
+            ok &= run is not step
+            for _ in range(3):
+                m = rng.standard_normal((n, d)).astype(np.float32)
+                x_in.copy_(local_rows(m * deg[:, None]))
+                b_in.copy_(local_rows(m))
+                run()
+                want = O.spmm_forward(g.indptr, g.indices, deg, m)
+                err = np.abs(f_out.cpu().numpy()[have] - want[mine[have]]) - (2e-6 + 2e-5 * np.abs(want[mine[have]]))
+                ok &= bool(err.max() <= 0)
+                conv = path[0]
+                wb = O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, m,
+                                               conv["numParts"])
+                err = np.abs(b_out.cpu().numpy()[have] - wb[mine[have]]) - (2e-6 + 2e-5 * np.abs(wb[mine[have]]))
+                ok &= bool(err.max() <= 0)
         # the sharded path sizes add up to the single-process ones
         sizes = torch.tensor([p["valid"] for p in hp.path] + [p["parts"] for p in hp.path], device=dev)
         dist.all_reduce(sizes)
@@ -89,13 +120,16 @@ def _worker(rank, world, port, mode, results):
         if hp.fabric is not None:
             hp.fabric.check()                         # no bounded wait ran out
             ok &= hp.fabric.count > 0
+            ok &= (int(hp.fabric.epoch.item()) > 0) == hp.streamed
         results[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.timeout(600)
-@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2", "balanced_halo:2:nccl"])
+@pytest.mark.parametrize("mode", ["balanced", "allgather", "halo", "balanced_halo", "balanced_halo:2", "balanced_halo:2:nccl",
+                                  "balanced_halo:1:push:graph", "balanced_halo:2:push:overlap", "balanced_halo:1:push:stream",
+                                  "balanced_halo:2:push:stream+graph"])
 def test_two_gpus_match_the_whole_graph_oracle(mode):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")

@@ -246,3 +246,31 @@ def test_group_kernel_writes_the_last_column_of_an_odd_row_into_an_aligned_view(
                                          conv["numParts"])
         assert_close(wide[:, :dim].cpu().numpy(), want, what=f"backward dim {dim} stride {stride}")
         assert (wide[:, dim:].cpu().numpy() == 7.0).all()
+
+
+@pytest.mark.parametrize("dim,left", [(16, 0), (22, 2), (5, 3), (64, 0)])
+@pytest.mark.parametrize("graph", ["hubs", "loops"])
+def test_an_edge_list_cut_into_three_plans_adds_up(cuda, graph, dim, left):
+    """The edge list cut by source id into three plans over the same rows: the first stored, the others
+    added (the aggregation of a row exchange that is read owner by owner)."""
+    indptr, indices = random_csr(**GRAPHS[graph])
+    n = len(indptr) - 1
+    rng = np.random.Generator(np.random.PCG64(dim))
+    feat = rng.standard_normal((n, dim)).astype(np.float32)
+    deg = degrees_of(indptr)
+    src = padded_rows(feat * deg[:, None], cuda)
+    rows = np.repeat(np.arange(n, dtype=np.int32), np.diff(indptr))
+    part = indices % 3
+    wide = torch.full((n, left + dim + 1), 7.0, device=cuda)
+    out = wide[:, left:left + dim]
+    for k in range(3):
+        pick = part == k
+        plan = capi.TilePlan.from_ids(t(rows[pick], cuda), t(indices[pick].astype(np.int32), cuda), int(pick.sum()), n)
+        if k == 0:
+            capi.spmm_tiles(src, plan, t(deg, cuda), out=out)
+        else:
+            capi.spmm_tiles_add(src, plan, t(deg, cuda), out)
+    torch.cuda.synchronize()
+    assert_close(out.cpu().numpy(), O.spmm_forward(indptr, indices, deg, feat), 2e-5, 2e-6, what="three plans")
+    full = wide.cpu().numpy()
+    assert (full[:, :left] == 7.0).all() and (full[:, left + dim:] == 7.0).all()

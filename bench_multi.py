@@ -105,11 +105,23 @@ def run_bench(args, rank: int, world: int, dev):
     ``WORKLOADS`` entry is too large for the host generator are drawn on the GPU
     (every rank draws the same graph from the same seed)."""
     if not dist.is_initialized():
-        if "MASTER_ADDR" in os.environ:
-            dist.init_process_group("nccl", device_id=dev)
-        else:       # plain `python bench.py` with a device-drawn workload: a group of one
-            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1,
-                                    device_id=dev)
+        # NCCL announces its version on the process's standard output when the communicator is made; the only
+        # line this program may print there is the result, so the descriptor points at standard error meanwhile
+        import sys
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            if "MASTER_ADDR" in os.environ:
+                dist.init_process_group("nccl", device_id=dev)
+            else:       # plain `python bench.py` with a device-drawn workload: a group of one
+                dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1,
+                                        device_id=dev)
+            dist.barrier()
+            torch.cuda.synchronize()
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
     spec = graphs.WORKLOADS[args.workload]
     device_drawn = spec.get("draw") == "device"
     t0 = time.perf_counter()

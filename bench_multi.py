@@ -98,6 +98,52 @@ def check_shard(hp, ops, staged, local_in, outs, one, dev, rank, world, rows_wan
             "rank0_per_aggregation": detail}
 
 
+def check_shard_on_device(hp, ops, staged, local_in, outs, one, dev, rank, world):
+    """The parity check of a workload that is drawn on the GPU and too large for the host oracle: every
+    aggregation of the epoch is run once more and ALL of this rank's result rows are compared with a float64
+    sparse product computed on the device by torch (cuSPARSE) from the rank's own CSR shard / compacted edge
+    list and the input rows of all ranks -- an implementation that shares nothing with this library's
+    kernels or exchange.  Tolerance |got - want| <= 2e-6 + 2e-5 |want|.  Returns the `check` object."""
+    n_loc, n = hp.n_loc, hp.n
+    deg = hp.deg.double()
+    deg_row = hp.deg_row.double()
+    worst, detail = -float("inf"), {}
+    fwd = torch.sparse_csr_tensor(hp.row, hp.col, torch.ones(hp.col.numel(), dtype=torch.float64, device=dev),
+                                  size=(n_loc, n))
+    for k, (kind, i, d) in enumerate(ops):
+        mine = torch.cat([v for v in staged[k]], dim=1).contiguous() if local_in[k] is None else local_in[k].contiguous()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        x = torch.cat(parts, dim=0).double()                       # rows in the partition's numbering
+        del parts
+        one(k)
+        torch.cuda.synchronize()
+        if kind == "fwd":
+            want = torch.sparse.mm(fwd, x)
+        else:
+            p = hp.path[i]
+            v = p["valid"]
+            back = torch.sparse_coo_tensor(torch.stack([p["id"][:v].long(), p["edges"][:v].long()]),
+                                           torch.ones(v, dtype=torch.float64, device=dev), size=(n_loc, n))
+            want = torch.sparse.mm(back.coalesce(), x * deg[:x.size(0), None])
+            del back
+        want *= deg_row[:, None]
+        excess = float(((outs[k].double() - want).abs() - (2e-6 + 2e-5 * want.abs())).max().item())
+        del want, x
+        detail[f"{kind}_l{i + 1}"] = excess
+        worst = max(worst, excess)
+    del fwd
+    torch.cuda.empty_cache()
+    t = torch.tensor([worst], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if hp.fabric is not None:
+        hp.fabric.check()
+    return {"rows_per_rank": int(n_loc), "max_excess": float(t.item()), "ok": bool(t.item() <= 0),
+            "tolerance": "|got-want| <= 2e-6 + 2e-5|want| against a float64 cuSPARSE product on the device, every "
+                         "row of every rank",
+            "rank0_per_aggregation": detail}
+
+
 def run_bench(args, rank: int, world: int, dev):
     """Multi-GPU arm of bench.py: the forward and backward aggregations of every
     layer, row-partitioned, each preceded by the exchange of its source rows.
@@ -255,11 +301,12 @@ def run_bench(args, rank: int, world: int, dev):
         hp.fabric.check()
 
     # parity of what was timed, outside the timed region: every aggregation's local result on sampled
-    # rows against the float64 oracle of this rank's shard (host-drawn workloads; the device-drawn graph
-    # is too large for a host oracle)
+    # rows against the float64 oracle of this rank's shard (host-drawn workloads), or on all rows against a
+    # float64 sparse product on the device (the device-drawn graph is too large for a host oracle)
     check = None
-    if not device_drawn and mode in ("balanced", "balanced_halo") and not getattr(args, "no_check", False):
-        check = check_shard(hp, ops, staged, local_in, outs, one, dev, rank, world)
+    if mode in ("balanced", "balanced_halo") and not getattr(args, "no_check", False):
+        check = (check_shard_on_device if device_drawn else check_shard)(hp, ops, staged, local_in, outs, one, dev,
+                                                                         rank, world)
 
     # e2e: host buffers, every step stages this rank's rows in and its results out
     host_in = [[torch.empty(x.shape, pin_memory=True).copy_(x) for x in views] for views in staged]

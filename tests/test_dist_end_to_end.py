@@ -283,6 +283,8 @@ def _worker(rank, world, port, mode, results):
                     hp.backward(i, full, d_in)
                 ok &= close(d_in, O.ours_backward_aggregate(conv["id"], conv["partPointer"], conv["edgeList"], deg, m,
                                                             conv["numParts"]))
+        step = lambda: None                          # noqa: E731
+        ok &= hp.graphed(step) is step                # nothing to capture without a CUDA device
         if parts[2:3] == ["push"]:
             ok &= isinstance(hp.fabric, SharedFileFabric) and hp.fabric.count > 0
             ok &= hp.fabric.signals > 0 if streamed else hp.fabric.signals == 0

@@ -31,3 +31,13 @@ def test_reference_arm_runs_on_rank_zero_only():
                 env={"RANK": "1", "WORLD_SIZE": "2"}) == []
     (line,) = _run("--impl", "reference", "--workload", "rmat24")
     assert line == {"impl": "reference", "unavailable": line["unavailable"]} and "GPU" in line["unavailable"]
+
+
+def test_small_workloads_are_timed_behind_an_l2_flush():
+    """A workload whose forward inputs would stay in the 126 MB L2 from one step to the next is timed
+    behind a flush; the large ones read more than L2 holds.  Both arms print the same wording."""
+    import bench
+    note, fits = bench.l2_policy(2708, 13264, [16, 22])
+    assert fits and "flushed" in note
+    note, fits = bench.l2_policy(2_097_152, 35_651_584, [16, 22])
+    assert not fits and "exceed" in note

@@ -266,7 +266,18 @@ def run_bench(args, rank: int, world: int, dev):
     # --no-graph is given: a dozen small submissions per aggregation otherwise let the ranks drift apart on
     # the host, and every barrier then waits for the slowest submitter.
     graphed = dealt and not getattr(args, "no_graph", False) and (world == 1 or hp.fabric is not None)
-    run = hp.graphed(step) if graphed else step
+    run = step
+    if graphed:
+        try:
+            run = hp.graphed(step)
+        except Exception as exc:              # noqa: BLE001 - any capture failure means "submit the launches one by one"
+            B.log(f"[bench] rank {rank}: graph capture failed ({exc!r}); timing separate submissions")
+            run = step
+        # every rank replays the same thing: if the capture failed anywhere, nobody uses a graph
+        agreed = torch.tensor([0 if run is step else 1], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            run, graphed = step, False
 
     stream = torch.cuda.current_stream()
     with B.ClockSampler(dev.index) as clocks:

@@ -5,8 +5,8 @@
 // flag barrier with bounded waits orders the pushes against the readers'
 // kernels.  The reference is single-GPU and has no counterpart of this file.
 //
-// Only plain loads and stores touch peer memory here: no bulk/TMA copies, no
-// multicast.  Every wait has an iteration limit; when it runs out the kernel
+// Only plain per-thread loads and stores touch peer memory here, each addressed
+// to one GPU.  Every wait has an iteration limit; when it runs out the kernel
 // records EPP_ERR_PEER_TIMEOUT in a status word and returns.
 #include "rowio.cuh"
 

@@ -19,7 +19,11 @@ ways of choosing and exchanging them are kept, selected by ``exchange``:
                  kernel of this package that gathers the rows and stores them
                  straight into the readers' buffers over NVLink, ordered by a flag
                  barrier with bounded waits (``PeerFabric``); NCCL all-to-all is the
-                 alternative transport.
+                 alternative transport.  The barrier numbers itself on the device,
+                 so a whole step can be captured into one CUDA graph and replayed
+                 (``DistHotPath.graphed``).  ``streamed=True`` replaces push + barrier
+                 + one aggregation by a push that signals every peer as its rows are
+                 complete and an aggregation cut by source owner.
 
 Per layer (``all-gather`` stands for whichever exchange the mode uses):
 
